@@ -2,7 +2,7 @@
 
 Cache entries (one per layer call that writes keys and values) with the same key/value
 shape and window form a *group*. A group has one arena
-``[entries, 2 (K|V), pages + 1, kv_heads, page_size, head_dim]`` and one pool of page ids
+``[entries, planes (K|V, or one), pages + 1, kv_heads, page_size, head_dim]`` and one pool of page ids
 shared by its entries, as the reference gives each group its own pool and tables
 (python/instinct/paged_kv.py:156-202; python/instinct/backends/dense.py:57-70). Inside a
 page the layout is head-major, so one (page, kv head) tile is ``page_size * head_dim``
@@ -38,7 +38,7 @@ class CacheGroup:
     arena: torch.Tensor | None = None
 
     def bytes_per_token(self, element_size: int) -> int:
-        return 2 * len(self.entries) * self.spec.kv_heads * self.spec.head_dim * element_size
+        return self.spec.planes * len(self.entries) * self.spec.kv_heads * self.spec.head_dim * element_size
 
 
 def plan_groups(cache_specs: dict[int, KVCacheSpec | StateSpec]) -> tuple[list[CacheGroup], dict[int, StateSpec]]:
@@ -51,6 +51,8 @@ def plan_groups(cache_specs: dict[int, KVCacheSpec | StateSpec]) -> tuple[list[C
             continue
         if spec not in groups:
             name = f"window{spec.window}" if spec.window else "full"
+            if spec.planes != 2:
+                name += f"_x{spec.planes}"
             if any(g.name == name for g in groups.values()):
                 name = f"{name}_h{spec.kv_heads}d{spec.head_dim}"
             groups[spec] = CacheGroup(len(groups), name, spec, [])
@@ -121,7 +123,7 @@ class PagedCache:
         for group in self.groups:
             spec = group.spec
             group.arena = torch.zeros(
-                (len(group.entries), 2, group.capacity_pages + 1, spec.kv_heads, page_size, spec.head_dim),
+                (len(group.entries), spec.planes, group.capacity_pages + 1, spec.kv_heads, page_size, spec.head_dim),
                 dtype=dtype,
                 device=self.device,
             )
@@ -185,7 +187,7 @@ class PagedCache:
         group, slot = self.entry_group[cache_id]
         arenas = self._entry_arenas.get(cache_id)
         if arenas is None:  # the arena never moves: slice it once per entry, not once per layer and step
-            arenas = self._entry_arenas[cache_id] = (group.arena[slot, 0], group.arena[slot, 1])
+            arenas = self._entry_arenas[cache_id] = (group.arena[slot, 0], group.arena[slot, 1] if group.spec.planes > 1 else None)
         return CacheView(
             cache_id=cache_id,
             writes=writes,

@@ -1,3 +1,4 @@
+from .gunedra_config import GunedraConfig
 from .model_config import ConfigError, ModelConfig, Qwen2Config, read_config_json
 from .registry import (
     Architecture,
@@ -10,6 +11,7 @@ from .registry import (
 __all__ = [
     "Architecture",
     "ConfigError",
+    "GunedraConfig",
     "ModelConfig",
     "Qwen2Config",
     "parse_config",

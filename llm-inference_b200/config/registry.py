@@ -44,6 +44,8 @@ def registered_architectures() -> tuple[str, ...]:
 
 def resolve_architecture(raw_config: dict[str, Any]) -> Architecture:
     names = raw_config.get("architectures") or []
+    if not names and isinstance(raw_config.get("architecture"), str):
+        names = [raw_config["architecture"]]  # some checkpoints name their one architecture in a plain string
     if names:
         name = names[0]
         if name not in _ARCHITECTURES:

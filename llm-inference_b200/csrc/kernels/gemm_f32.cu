@@ -37,9 +37,13 @@ __device__ __forceinline__ void load_tile(const float* __restrict__ src, int row
 __global__ void __launch_bounds__(kGemmThreads)
 gemm_f32_kernel(const float* __restrict__ A, const float* __restrict__ W,
                 const float* __restrict__ bias, float* __restrict__ C, int M, int N, int K,
-                int lda, int ldw, int ldc, bool vec) {
+                int lda, int ldw, int ldc, bool vec, int64_t batch_a, int64_t batch_w, int64_t batch_c) {
   __shared__ float As[BK][BM + 4];
   __shared__ float Ws[BK][BN + 4];
+  // One product per blockIdx.z: the operands of product b start b strides further on.
+  A += blockIdx.z * batch_a;
+  W += blockIdx.z * batch_w;
+  C += blockIdx.z * batch_c;
   const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
   const int ty = threadIdx.x / (BN / TN), tx = threadIdx.x % (BN / TN);
   float acc[TM][TN];
@@ -90,6 +94,23 @@ B200_API int b200_gemm_f32(const float* A, const float* W, const float* bias, fl
                    (reinterpret_cast<uintptr_t>(W) % 16 == 0);
   const dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
   B200_REQUIRE(grid.y <= 65535, "gemm_f32: too many rows (%d)", M);
-  gemm_f32_kernel<<<grid, kGemmThreads, 0, stream>>>(A, W, bias, C, M, N, K, lda, ldw, ldc, vec);
+  gemm_f32_kernel<<<grid, kGemmThreads, 0, stream>>>(A, W, bias, C, M, N, K, lda, ldw, ldc, vec, 0, 0, 0);
   return b200_check_launch("gemm_f32");
+}
+
+// `batch` products of the same shape in one launch: C_b = A_b * W_b^T, each operand's b-th
+// matrix `stride_*` elements after the first (a head's slice of a wider row, for instance).
+B200_API int b200_gemm_f32_batched(const float* A, const float* W, float* C, int M, int N, int K, int lda, int ldw, int ldc,
+                                   int batch, int64_t stride_a, int64_t stride_w, int64_t stride_c, cudaStream_t stream) {
+  if (M == 0 || N == 0 || batch == 0) return 0;
+  B200_REQUIRE(M > 0 && N > 0 && K > 0 && batch > 0 && batch <= 65535, "gemm_f32_batched: bad sizes %d x %d x %d x %d", batch, M,
+               N, K);
+  B200_REQUIRE(lda >= K && ldw >= K && ldc >= N, "gemm_f32_batched: leading dimensions too small");
+  const bool vec = (K % 4 == 0) && (lda % 4 == 0) && (ldw % 4 == 0) && (stride_a % 4 == 0) && (stride_w % 4 == 0) &&
+                   (reinterpret_cast<uintptr_t>(A) % 16 == 0) && (reinterpret_cast<uintptr_t>(W) % 16 == 0);
+  const dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM, batch);
+  B200_REQUIRE(grid.y <= 65535, "gemm_f32_batched: too many rows (%d)", M);
+  gemm_f32_kernel<<<grid, kGemmThreads, 0, stream>>>(A, W, nullptr, C, M, N, K, lda, ldw, ldc, vec, stride_a, stride_w,
+                                                     stride_c);
+  return b200_check_launch("gemm_f32_batched");
 }

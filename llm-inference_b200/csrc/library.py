@@ -68,6 +68,20 @@ _SIGNATURES: dict[str, list] = {
                               c_void_p, c_int, c_int, c_float, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
     "b200_argmax_rows": [c_void_p, c_int, c_int, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
     "b200_sample_rows": [c_void_p, c_int, c_int, c_int64] + [c_void_p] * 7 + [c_void_p, c_int64, c_void_p],
+    "b200_gemm_f32_batched": [c_void_p] * 3 + [c_int] * 7 + [c_int64] * 3 + [c_void_p],
+    "b200_branch_norm_add": [c_void_p] * 4 + [c_float, c_int, c_int, c_int, c_float, c_void_p, c_void_p, c_void_p, c_int64,
+                             c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p],
+    "b200_grouped_rmsnorm": [c_void_p] * 3 + [c_int, c_int, c_int, c_float, c_void_p, c_int, c_void_p],
+    "b200_embedding_scaled": [c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
+    "b200_poly_norm": [c_void_p, c_void_p, c_int, c_int, c_float, c_void_p, c_int, c_void_p],
+    "b200_latent_kv_write": [c_void_p] + [c_int] * 8 + [c_void_p, c_float, c_void_p, c_int] + [c_void_p] * 3 + [c_int, c_int,
+                             c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p],
+    "b200_latent_attention_plain": [c_void_p, c_int64, c_int64] + [c_void_p] * 5 + [c_int, c_int, c_void_p, c_void_p, c_int64,
+                                    c_void_p, c_int64, c_int64] + [c_int] * 6 + [c_float, c_int, c_void_p, c_void_p],
+    "b200_delta_prepare": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int] + [c_void_p] * 7 + [c_int] * 6 + [c_void_p] * 5
+                          + [c_int, c_void_p],
+    "b200_delta_recurrence": [c_void_p] * 8 + [c_int] * 5 + [c_void_p] * 3,
+    "b200_delta_output": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_void_p, c_int, c_void_p],
 }
 
 

@@ -64,3 +64,21 @@ def attend(
             ctx, cache, q, out, q_heads, kv_heads, head_dim, scale,
             first_seq=decode_seqs, num_seqs=ctx.num_seqs - decode_seqs, decode=False, max_q_len=ctx.max_q_len,
         )
+
+
+def attend_latent(
+    ctx: StepContext,
+    cache: CacheView,
+    q_lat: torch.Tensor,
+    q_rot: torch.Tensor,
+    sink: torch.Tensor | None,
+    gate: torch.Tensor | None,
+    out: torch.Tensor,
+    heads: int,
+    rank: int,
+    rot_dim: int,
+    scale: float,
+) -> None:
+    """Attention over cached latents (parts/latent_attention.py): the plain kernel, which takes
+    float32 and every shape."""
+    ops.latent_attention_plain(ctx, cache, q_lat, q_rot, sink, gate, out, heads, rank, rot_dim, scale)

@@ -40,11 +40,14 @@ from ..weights.loader import TensorSpec
 
 @dataclass(frozen=True)
 class KVCacheSpec:
-    """Paged keys and values: ``window`` 0 keeps every position, else the last ``window``."""
+    """Paged keys and values: ``window`` 0 keeps every position, else the last ``window``.
+    ``planes`` 1 keeps one row per token instead of a key row and a value row (a mixer whose
+    values are read out of its key rows, such as attention over cached latents)."""
 
     kv_heads: int
     head_dim: int
     window: int = 0
+    planes: int = 2
 
 
 @dataclass(frozen=True)

@@ -69,4 +69,84 @@ class PreNormResidualBlock(Part):
         return norm.forward(ctx, x, delta)
 
 
+class PostNormResidualBlock(Part):
+    """``x += mult * scale1 * norm1(mixer(x)); x += mult * scale2 * norm2(feed_forward(x))``: the
+    branches read the stream itself and the norms act on what they return. ``scale1`` / ``scale2``
+    are learned per-column factors (None: ones), ``feed_forward`` may be None.
+
+    With ``depth_mix`` = ``{"tensor": name, "index": i, "layers": L}`` the layer hands on, instead of
+    its result, a weighted average over depth: with X_0 the embedding's output and X_(j+1) the
+    result of layer j (before any averaging), layer ``i`` passes ``sum_{j <= i+1} w[j] X_j`` to what
+    follows, ``w`` being the ``i + 2`` numbers of the named tensor. The X_j of a step live in one
+    workspace buffer ``[L + 1, tokens, hidden]``; layer 0 also files the stream it receives as X_0.
+
+    Every add, norm and average is one kernel per branch (``GroupedRMSNorm.add_branch``), which also
+    writes the stream rounded to the compute dtype (buffer ``stream_cast``), the operand of the next
+    matrix product; in 32-bit the stream is its own operand. The block never leaves a pending
+    branch output: it returns None."""
+
+    def __init__(self, *, mixer: PartSpec, feed_forward: PartSpec | None, mixer_norm: PartSpec, feed_forward_norm: PartSpec | None,
+                 hidden_size: int, mult: float = 1.0, mixer_scale: str | None = None, feed_forward_scale: str | None = None,
+                 depth_mix: dict | None = None) -> None:
+        self.hidden_size, self.mult = hidden_size, float(mult)
+        self.mixer_norm = build_part("norm", mixer_norm)
+        self.mixer = build_part("mixer", mixer)
+        self.feed_forward = build_part("feed_forward", feed_forward) if feed_forward is not None else None
+        self.feed_forward_norm = build_part("norm", feed_forward_norm) if feed_forward is not None else None
+        self.parts = tuple(p for p in (self.mixer_norm, self.mixer, self.feed_forward_norm, self.feed_forward) if p is not None)
+        self.graph_safe = all(p.graph_safe for p in self.parts)
+        self.scale_names = (mixer_scale, feed_forward_scale if feed_forward is not None else None)
+        self.scales: list[torch.Tensor | None] = [None, None]
+        self.depth_mix = dict(depth_mix) if depth_mix else None
+        self.mix: torch.Tensor | None = None
+
+    def tensor_specs(self):
+        from ..weights.loader import TensorSpec
+
+        specs = [spec for part in self.parts for spec in part.tensor_specs()]
+        specs += [TensorSpec(name, (self.hidden_size,), init="one_plus_normal") for name in self.scale_names if name]
+        if self.depth_mix:
+            specs.append(TensorSpec(self.depth_mix["tensor"], (self.depth_mix["index"] + 2,), init="half_plus_normal"))
+        return specs
+
+    def load(self, tensors, dtype, device) -> None:
+        for part in self.parts:
+            part.load(tensors, dtype, device)
+        self.scales = [tensors[name].to(device=device, dtype=torch.float32).contiguous() if name else None for name in self.scale_names]
+        if self.depth_mix:
+            self.mix = tensors[self.depth_mix["tensor"]].to(device=device, dtype=torch.float32).contiguous()
+
+    def weight_bytes(self) -> int:
+        return sum(part.weight_bytes() for part in self.parts) + sum(4 * s.numel() for s in self.scales if s is not None)
+
+    def cache_spec(self):
+        return self.mixer.cache_spec()
+
+    def forward(self, ctx: StepContext, cache: CacheView | None, x: torch.Tensor, delta):
+        if delta is not None:
+            raise ValueError("a post-norm block reads a stream that is up to date")
+        tokens = ctx.num_tokens
+        rounded = ctx.dtype != torch.float32
+        cast = ctx.buffer("stream_cast", (tokens, self.hidden_size)) if rounded else None
+        history = result = None
+        mix = {}
+        if self.depth_mix:
+            index = self.depth_mix["index"]
+            history = ctx.buffer("depth_history", (self.depth_mix["layers"] + 1, tokens, self.hidden_size), torch.float32, per_token=False)
+            result = history[index + 1]
+            mix = dict(history=history, mix=self.mix, mixed=x)
+        else:
+            result = x
+        keep = history[0] if history is not None and self.depth_mix["index"] == 0 else None
+        branch = self.mixer.forward(ctx, cache, cast if rounded else x)
+        if self.feed_forward is None:
+            self.mixer_norm.add_branch(ctx, x, branch, self.scales[0], self.mult, result, copy_in=keep, cast=cast, **mix)
+            return None
+        self.mixer_norm.add_branch(ctx, x, branch, self.scales[0], self.mult, result, copy_in=keep, cast=cast)
+        branch = self.feed_forward.forward(ctx, cast if rounded else result)
+        self.feed_forward_norm.add_branch(ctx, result, branch, self.scales[1], self.mult, result, cast=cast, **mix)
+        return None
+
+
 register_part("block", "pre_norm_residual", PreNormResidualBlock)
+register_part("block", "post_norm_residual", PostNormResidualBlock)

@@ -11,42 +11,52 @@ from .context import StepContext
 
 
 class TokenEmbedding(Part):
-    """``x[t] = table[token[t]]`` widened to the 32-bit residual stream
-    (python/instinct/backends/dense.py:82)."""
+    """``x[t] = table[token[t]] * scale`` widened to the 32-bit residual stream
+    (python/instinct/backends/dense.py:82; ``scale`` is 1 there). ``suffix`` is what follows
+    ``name`` in the checkpoint's tensor name. With ``cast`` the step also gets the stream rounded
+    to the compute dtype (buffer ``stream_cast``), which layers whose branches read the stream
+    itself, without a norm in front, hand to their matrix products."""
 
-    def __init__(self, *, name: str, vocab_size: int, hidden_size: int) -> None:
+    def __init__(self, *, name: str, vocab_size: int, hidden_size: int, scale: float = 1.0, suffix: str = ".weight",
+                 cast: bool = False) -> None:
         self.name, self.vocab_size, self.hidden_size = name, vocab_size, hidden_size
+        self.scale, self.suffix, self.cast = float(scale), suffix, bool(cast)
         self.table: torch.Tensor | None = None
 
     def tensor_specs(self) -> list[TensorSpec]:
-        return [TensorSpec(self.name + ".weight", (self.vocab_size, self.hidden_size))]
+        return [TensorSpec(self.name + self.suffix, (self.vocab_size, self.hidden_size))]
 
     def load(self, tensors, dtype, device) -> None:
-        self.table = tensors[self.name + ".weight"].to(device=device, dtype=dtype).contiguous()
+        self.table = tensors[self.name + self.suffix].to(device=device, dtype=dtype).contiguous()
 
     def weight_bytes(self) -> int:
         return 0  # a step reads only its tokens' rows
 
     def forward(self, ctx: StepContext) -> torch.Tensor:
         x = ctx.buffer("residual", (ctx.num_tokens, self.hidden_size), torch.float32)
-        return ops.embedding_gather(ctx, self.table, x)
+        if self.scale == 1.0 and not self.cast:
+            return ops.embedding_gather(ctx, self.table, x)
+        rounded = self.cast and self.table.dtype != torch.float32  # in 32-bit the stream is its own copy
+        cast = ctx.buffer("stream_cast", (ctx.num_tokens, self.hidden_size), self.table.dtype) if rounded else None
+        return ops.embedding_scaled(ctx, self.table, self.scale, x, cast)
 
 
 class OutputHead(Part):
     """``logits = h W^T`` in 32-bit. With ``tied_to`` the matrix is the embedding table and
     the checkpoint need not hold a tensor of its own (python/instinct/export.py:38-41)."""
 
-    def __init__(self, *, name: str, vocab_size: int, hidden_size: int, tied_to: str | None = None) -> None:
+    def __init__(self, *, name: str, vocab_size: int, hidden_size: int, tied_to: str | None = None, suffix: str = ".weight") -> None:
         self.name, self.vocab_size, self.hidden_size, self.tied_to = name, vocab_size, hidden_size, tied_to
+        self.suffix = suffix
         self.weight: torch.Tensor | None = None
 
     def tensor_specs(self) -> list[TensorSpec]:
-        return [TensorSpec(self.name + ".weight", (self.vocab_size, self.hidden_size), optional=self.tied_to is not None)]
+        return [TensorSpec(self.name + self.suffix, (self.vocab_size, self.hidden_size), optional=self.tied_to is not None)]
 
     def load(self, tensors, dtype, device) -> None:
-        own = tensors.get(self.name + ".weight")
+        own = tensors.get(self.name + self.suffix)
         if own is None:
-            own = tensors[self.tied_to + ".weight"]
+            own = tensors[self.tied_to + self.suffix]
         self.weight = own.to(device=device, dtype=dtype).contiguous()
 
     def share(self, embedding: TokenEmbedding) -> None:

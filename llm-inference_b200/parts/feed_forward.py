@@ -53,4 +53,34 @@ class SwiGLU(Part):
         return ops.linear(ctx, act, self.w_down, ctx.buffer("branch", (t, self.hidden_size)))
 
 
+class PolyNormFeedForward(Part):
+    """``down(act(up(h)))`` without biases, ``act(z) = a N(z) + b N(z^2) + c N(z^3) + e`` with powers
+    taken element by element and ``N`` dividing a token's row by its root mean square
+    (``eps`` inside the root); ``a, b, c, e`` are the four numbers of the ``act`` tensor."""
+
+    def __init__(self, *, prefix: str, hidden_size: int, intermediate_size: int, eps: float) -> None:
+        self.prefix, self.hidden_size, self.intermediate_size, self.eps = prefix, hidden_size, intermediate_size, float(eps)
+        self.w_up = self.w_down = self.coefficients = None
+
+    def tensor_specs(self) -> list[TensorSpec]:
+        p, h, i = self.prefix, self.hidden_size, self.intermediate_size
+        return [TensorSpec(f"{p}up", (i, h)), TensorSpec(f"{p}down", (h, i)), TensorSpec(f"{p}act", (4,), init="half_plus_normal")]
+
+    def load(self, tensors, dtype, device) -> None:
+        p = self.prefix
+        self.w_up = tensors[f"{p}up"].to(device=device, dtype=dtype).contiguous()
+        self.w_down = tensors[f"{p}down"].to(device=device, dtype=dtype).contiguous()
+        self.coefficients = tensors[f"{p}act"].to(device=device, dtype=torch.float32).contiguous()
+
+    def weight_bytes(self) -> int:
+        return (self.w_up.numel() + self.w_down.numel()) * self.w_down.element_size()
+
+    def forward(self, ctx: StepContext, h: torch.Tensor) -> torch.Tensor:
+        t, i = ctx.num_tokens, self.intermediate_size
+        z = ops.linear(ctx, h, self.w_up, ctx.buffer("ff_up", (t, i)))
+        act = ops.poly_norm(ctx, z, self.coefficients, self.eps, ctx.buffer("act", (t, i)))
+        return ops.linear(ctx, act, self.w_down, ctx.buffer("branch", (t, self.hidden_size)))
+
+
 register_part("feed_forward", "swiglu", SwiGLU)
+register_part("feed_forward", "poly_norm", PolyNormFeedForward)

@@ -55,4 +55,44 @@ class RMSNorm(Part):
         return ops.rmsnorm(ctx, x, delta, self.weight, self.eps, out, rows)
 
 
+class GroupedRMSNorm(Part):
+    """RMS norm in groups: the row is cut into ``groups`` equal consecutive parts, each divided by
+    its own ``sqrt(mean(part^2) + eps)``, and the whole is multiplied by the weight; all 32-bit.
+
+    Two uses. As the norm of the stream itself (``forward``, the interface of every norm part; the
+    model's last norm). And as the norm of a branch's *output* in a layer that adds
+    ``mult * scale * norm(branch(x))`` to its stream (``add_branch``); the same kernel can then also
+    form the weighted average over depth that such a layer hands on (parts/block.py)."""
+
+    foldable = False
+
+    def __init__(self, *, name: str, hidden_size: int, groups: int, eps: float) -> None:
+        if groups <= 0 or hidden_size % groups:
+            raise ValueError(f"{hidden_size} columns do not cut into {groups} equal groups")
+        self.name, self.hidden_size, self.groups, self.eps = name, hidden_size, int(groups), float(eps)
+        self.weight: torch.Tensor | None = None
+
+    def tensor_specs(self) -> list[TensorSpec]:
+        return [TensorSpec(self.name, (self.hidden_size,), init="one_plus_normal")]
+
+    def load(self, tensors, dtype, device) -> None:
+        self.weight = tensors[self.name].to(device=device, dtype=torch.float32).contiguous()
+
+    def weight_bytes(self) -> int:
+        return self.weight.numel() * 4
+
+    def forward(self, ctx: StepContext, x: torch.Tensor, delta, rows: torch.Tensor | None = None, out_name: str = "normed",
+                folded_ok: bool = False) -> torch.Tensor:
+        if delta is not None:
+            raise ValueError("a grouped norm reads a stream that is up to date; it takes no pending branch output")
+        count = x.shape[0] if rows is None else rows.shape[0]
+        out = ctx.buffer(out_name, (count, self.hidden_size), per_token=rows is None)
+        return ops.grouped_rmsnorm(ctx, x, self.weight, self.groups, self.eps, out, rows)
+
+    def add_branch(self, ctx: StepContext, x_in: torch.Tensor, branch: torch.Tensor, scale: torch.Tensor | None, mult: float,
+                   x_out: torch.Tensor, **more) -> None:
+        ops.branch_norm_add(ctx, x_in, branch, self.weight, scale, mult, self.groups, self.eps, x_out, **more)
+
+
 register_part("norm", "rmsnorm", RMSNorm)
+register_part("norm", "grouped_rmsnorm", GroupedRMSNorm)

@@ -540,3 +540,208 @@ def argmax_rows(lib, logits: torch.Tensor, out: torch.Tensor, row_index: torch.T
         "b200_argmax_rows", ptr(logits), c_int(rows), c_int(logits.shape[1]), c_int64(logits.stride(0)),
         ptr(row_index), ptr(out), ptr(None), ptr(None), stream,
     )
+
+
+# -- norms on a branch's output, scaled embedding, PolyNorm --------------------------------------------
+
+
+def embedding_scaled(ctx: StepContext, table: torch.Tensor, scale: float, out: torch.Tensor, cast: torch.Tensor | None) -> torch.Tensor:
+    """``out[t] = table[token[t]] * scale`` in 32-bit; ``cast`` also receives it in the table's dtype."""
+    vocab, hidden = table.shape
+    _need(tuple(out.shape) == (ctx.num_tokens, hidden) and out.dtype == torch.float32, "embedding: bad output")
+    _need(cast is None or (cast.dtype == table.dtype and cast.shape == out.shape), "embedding: bad cast buffer")
+    ctx.lib.call(
+        "b200_embedding_scaled", ptr(table), ptr(ctx.token_ids), c_float(scale), ptr(out), ptr(cast), c_int(ctx.num_tokens),
+        c_int(hidden), c_int(vocab), c_int(dtype_code(table.dtype)), ptr(ctx.err), ctx.stream,
+    )
+    return out
+
+
+def branch_norm_add(
+    ctx: StepContext,
+    x_in: torch.Tensor,
+    branch: torch.Tensor,
+    weight: torch.Tensor,
+    scale: torch.Tensor | None,
+    mult: float,
+    groups: int,
+    eps: float,
+    x_out: torch.Tensor,
+    *,
+    copy_in: torch.Tensor | None = None,
+    history: torch.Tensor | None = None,
+    mix: torch.Tensor | None = None,
+    mixed: torch.Tensor | None = None,
+    cast: torch.Tensor | None = None,
+) -> None:
+    """``x_out = x_in + mult * scale * weight * branch / rms_groups(branch)``. With ``mix`` (``n`` weights) and
+    ``history`` (``[>= n, rows, hidden]``, whose slice ``n - 1`` is ``x_out``) also
+    ``mixed = sum_j mix[j] * history[j]``; ``cast`` receives the row that travels on (``mixed`` if there
+    is a mix, else ``x_out``) in the compute dtype; ``copy_in`` receives ``x_in`` unchanged."""
+    rows, hidden = x_in.shape
+    _need(x_in.dtype == torch.float32 and x_out.dtype == torch.float32 and x_in.is_contiguous() and x_out.is_contiguous(), "branch_norm_add: the stream is contiguous float32")
+    _need(tuple(branch.shape) == (rows, hidden) and branch.is_contiguous(), "branch_norm_add: bad branch output")
+    _need(weight.dtype == torch.float32 and weight.numel() == hidden, "branch_norm_add: weight must be float32 [hidden]")
+    _need(scale is None or (scale.dtype == torch.float32 and scale.numel() == hidden), "branch_norm_add: scale must be float32 [hidden]")
+    _need(cast is None or (cast.dtype == branch.dtype and cast.shape == x_in.shape), "branch_norm_add: bad cast buffer")
+    count = 0
+    stride = 0
+    if mix is not None:
+        count = mix.numel()
+        _need(mix.dtype == torch.float32 and mixed is not None and mixed.dtype == torch.float32 and mixed.shape == x_in.shape, "branch_norm_add: bad mix")
+        _need(history is not None and history.dtype == torch.float32 and history.is_contiguous() and history.shape[0] >= count, "branch_norm_add: bad history")
+        _need(history[count - 1].data_ptr() == x_out.data_ptr(), "branch_norm_add: the newest history entry is the output")
+        stride = history.stride(0)
+    ctx.lib.call(
+        "b200_branch_norm_add", ptr(x_in), ptr(branch), ptr(weight), ptr(scale), c_float(mult), c_int(rows), c_int(hidden),
+        c_int(groups), c_float(eps), ptr(x_out), ptr(copy_in), ptr(history), c_int64(stride), ptr(mix), c_int(count),
+        ptr(mixed), ptr(cast), c_int(dtype_code(branch.dtype)), ctx.stream,
+    )
+
+
+def grouped_rmsnorm(
+    ctx: StepContext, x: torch.Tensor, weight: torch.Tensor, groups: int, eps: float, out: torch.Tensor, rows: torch.Tensor | None = None
+) -> torch.Tensor:
+    hidden = x.shape[1]
+    num_rows = x.shape[0] if rows is None else rows.shape[0]
+    _need(x.dtype == torch.float32 and x.is_contiguous(), "grouped_rmsnorm: the stream is contiguous float32")
+    _need(weight.dtype == torch.float32 and weight.numel() == hidden, "grouped_rmsnorm: weight must be float32 [hidden]")
+    _need(tuple(out.shape) == (num_rows, hidden) and out.is_contiguous(), "grouped_rmsnorm: bad output shape")
+    ctx.lib.call(
+        "b200_grouped_rmsnorm", ptr(x), ptr(weight), ptr(rows), c_int(num_rows), c_int(hidden), c_int(groups), c_float(eps),
+        ptr(out), c_int(dtype_code(out.dtype)), ctx.stream,
+    )
+    return out
+
+
+def poly_norm(ctx: StepContext, z: torch.Tensor, coefficients: torch.Tensor, eps: float, out: torch.Tensor) -> torch.Tensor:
+    rows, width = z.shape
+    _need(z.is_contiguous() and out.is_contiguous() and out.shape == z.shape and out.dtype == z.dtype, "poly_norm: bad operands")
+    _need(coefficients.dtype == torch.float32 and coefficients.numel() == 4, "poly_norm: four float32 coefficients")
+    ctx.lib.call(
+        "b200_poly_norm", ptr(z), ptr(coefficients), c_int(rows), c_int(width), c_float(eps), ptr(out), c_int(dtype_code(z.dtype)),
+        ctx.stream,
+    )
+    return out
+
+
+def linear_per_head(ctx: StepContext, x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """``out[h] = x[h] @ weight[h].T`` for every head: ``x`` is ``[heads, rows, k]``, ``weight``
+    ``[heads, n, k]``, ``out`` ``[heads, rows, n]``; ``x`` and ``out`` may be views with any head and
+    row strides (a head's slice of wider rows) as long as their last dimension is dense. bfloat16
+    goes to the vendor library's batched product, float32 to this engine's FMA kernel."""
+    heads, rows, k = x.shape
+    n = weight.shape[1]
+    _need(tuple(weight.shape) == (heads, n, k) and weight.is_contiguous(), "linear_per_head: bad weight")
+    _need(tuple(out.shape) == (heads, rows, n) and x.stride(2) == 1 and out.stride(2) == 1, "linear_per_head: bad operands")
+    if rows == 0:
+        return out
+    if x.dtype == torch.float32:
+        _need(weight.dtype == torch.float32 and out.dtype == torch.float32, "linear_per_head: float32 path needs float32 operands")
+        ctx.lib.call(
+            "b200_gemm_f32_batched", ptr(x), ptr(weight), ptr(out), c_int(rows), c_int(n), c_int(k), c_int(x.stride(1)),
+            c_int(k), c_int(out.stride(1)), c_int(heads), c_int64(x.stride(0)), c_int64(n * k), c_int64(out.stride(0)),
+            ctx.stream,
+        )
+        return out
+    _need(x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and out.dtype == torch.bfloat16, "linear_per_head: bfloat16 path needs bfloat16 operands")
+    torch.bmm(x, weight.transpose(1, 2), out=out)
+    return out
+
+
+# -- attention over cached latents ------------------------------------------------------------------------
+
+
+def latent_kv_write(
+    ctx: StepContext, cache: CacheView, proj: torch.Tensor, q_offset: int, kv_offset: int, heads: int, dim: int, rot_dim: int,
+    rank: int, norm_weight: torch.Tensor, eps: float, inv_freq: torch.Tensor, q_rot: torch.Tensor,
+) -> None:
+    tokens, ld = proj.shape
+    _need(proj.is_contiguous() and cache.keys.dtype == proj.dtype and q_rot.dtype == proj.dtype, "latent_kv_write: bad operands")
+    _need(tuple(q_rot.shape) == (tokens, heads * rot_dim) and q_rot.is_contiguous(), "latent_kv_write: bad q_rot")
+    _need(norm_weight.dtype == torch.float32 and norm_weight.numel() == rank and inv_freq.dtype == torch.float32, "latent_kv_write: bad constants")
+    _need(tuple(cache.keys.shape[1:]) == (1, cache.page_size, rank + rot_dim), "latent_kv_write: the cache rows are [latent | rotated key part]")
+    ctx.lib.call(
+        "b200_latent_kv_write", ptr(proj), c_int(ld), c_int(q_offset), c_int(kv_offset), c_int(tokens), c_int(heads), c_int(dim),
+        c_int(rot_dim), c_int(rank), ptr(norm_weight), c_float(eps), ptr(inv_freq), c_int(2 * inv_freq.numel()),
+        ptr(ctx.positions), ptr(ctx.token_seq), ptr(cache.block_table), c_int(cache.max_pages), c_int(cache.num_pages),
+        ptr(cache.keys), c_int(cache.page_size), c_int(1 if cache.writes else 0), ptr(q_rot), c_int(dtype_code(proj.dtype)),
+        ptr(ctx.err), ctx.stream,
+    )
+
+
+def latent_attention_plain(
+    ctx: StepContext, cache: CacheView, q_lat: torch.Tensor, q_rot: torch.Tensor, sink: torch.Tensor | None,
+    gate: torch.Tensor | None, out: torch.Tensor, heads: int, rank: int, rot_dim: int, scale: float,
+) -> torch.Tensor:
+    """``q_lat`` and ``out`` are ``[heads, tokens, rank]`` views (any head and token strides), ``q_rot``
+    ``[tokens, heads * rot_dim]``, ``gate`` a ``[tokens, heads]`` view of logits with a dense last dimension."""
+    tokens = q_rot.shape[0]
+    _need(tuple(q_lat.shape) == (heads, tokens, rank) and q_lat.stride(2) == 1, "latent attention: bad q_lat")
+    _need(tuple(out.shape) == (heads, tokens, rank) and out.stride(2) == 1 and out.dtype == q_lat.dtype, "latent attention: bad output")
+    _need(q_rot.is_contiguous() and q_rot.dtype == q_lat.dtype and cache.keys.dtype == q_lat.dtype, "latent attention: dtypes differ")
+    _need(sink is None or (sink.dtype == torch.float32 and sink.numel() == heads), "latent attention: sink must be float32 [heads]")
+    _need(gate is None or (tuple(gate.shape) == (tokens, heads) and gate.stride(1) == 1 and gate.dtype == q_lat.dtype), "latent attention: bad gate")
+    ctx.lib.call(
+        "b200_latent_attention_plain", ptr(q_lat), c_int64(q_lat.stride(1)), c_int64(q_lat.stride(0)), ptr(q_rot), ptr(cache.keys),
+        ptr(ctx.positions), ptr(ctx.token_seq), ptr(cache.block_table), c_int(cache.max_pages), c_int(cache.num_pages), ptr(sink),
+        ptr(gate), c_int64(gate.stride(0) if gate is not None else 0), ptr(out), c_int64(out.stride(1)), c_int64(out.stride(0)),
+        c_int(tokens), c_int(heads), c_int(rank), c_int(rot_dim), c_int(cache.page_size), c_int(cache.window), c_float(scale),
+        c_int(dtype_code(q_lat.dtype)), ptr(ctx.err), ctx.stream,
+    )
+    return out
+
+
+# -- the gated delta rule -----------------------------------------------------------------------------------
+
+
+def delta_prepare(
+    ctx: StepContext, proj: torch.Tensor, decay_in: torch.Tensor, taps: torch.Tensor, conv_state: torch.Tensor, a_log: torch.Tensor,
+    dt_bias: torch.Tensor, heads: int, kv_heads: int, dk: int, dv: int, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
+    beta: torch.Tensor, decay: torch.Tensor,
+) -> None:
+    """Convolution + silu of the q, k, v columns of ``proj`` (continuing each request's slot of
+    ``conv_state``, which is then moved on), unit vectors, beta and the decay factors, all 32-bit."""
+    tokens = proj.shape[0]
+    channels = 2 * kv_heads * dk + heads * dv
+    _need(proj.stride(1) == 1 and proj.shape[1] >= channels + heads, "delta_prepare: bad projections")
+    _need(decay_in.stride(1) == 1 and decay_in.shape[1] >= heads * dk and decay_in.dtype == proj.dtype, "delta_prepare: bad decay input")
+    _need(taps.dtype == torch.float32 and taps.shape[0] == channels and taps.is_contiguous(), "delta_prepare: taps are float32 [channels, taps]")
+    _need(conv_state.dtype == proj.dtype and tuple(conv_state.shape[1:]) == (max(taps.shape[1] - 1, 0), channels), "delta_prepare: bad convolution state")
+    for tensor, width in ((q, kv_heads * dk), (k, kv_heads * dk), (v, heads * dv), (beta, heads), (decay, heads * dk)):
+        _need(tensor.dtype == torch.float32 and tuple(tensor.shape) == (tokens, width) and tensor.is_contiguous(), "delta_prepare: bad output")
+    ctx.lib.call(
+        "b200_delta_prepare", ptr(proj), c_int(proj.stride(0)), ptr(decay_in), c_int(decay_in.stride(0)), ptr(taps),
+        c_int(taps.shape[1]), ptr(conv_state), ptr(a_log), ptr(dt_bias), ptr(ctx.token_seq), ptr(ctx.seq_q_start),
+        ptr(ctx.seq_q_len), ptr(ctx.seq_slot), c_int(tokens), c_int(ctx.num_seqs), c_int(heads), c_int(kv_heads), c_int(dk),
+        c_int(dv), ptr(q), ptr(k), ptr(v), ptr(beta), ptr(decay), c_int(dtype_code(proj.dtype)), ctx.stream,
+    )
+    ctx.lib.calls += 1  # the slot update is a launch of its own
+
+
+def delta_recurrence(
+    ctx: StepContext, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, beta: torch.Tensor, decay: torch.Tensor,
+    state: torch.Tensor, out: torch.Tensor, heads: int, kv_heads: int, dk: int, dv: int,
+) -> torch.Tensor:
+    _need(state.dtype == torch.float32 and tuple(state.shape[1:]) == (heads, dk, dv) and state.is_contiguous(), "delta_recurrence: the state is float32 [slots, heads, dk, dv]")
+    _need(out.dtype == torch.float32 and tuple(out.shape) == (q.shape[0], heads * dv) and out.is_contiguous(), "delta_recurrence: bad output")
+    ctx.lib.call(
+        "b200_delta_recurrence", ptr(q), ptr(k), ptr(v), ptr(beta), ptr(decay), ptr(ctx.seq_q_start), ptr(ctx.seq_q_len),
+        ptr(ctx.seq_slot), c_int(ctx.num_seqs), c_int(heads), c_int(kv_heads), c_int(dk), c_int(dv), ptr(state), ptr(out),
+        ctx.stream,
+    )
+    return out
+
+
+def delta_output(
+    ctx: StepContext, o: torch.Tensor, weight: torch.Tensor, gate: torch.Tensor, heads: int, dv: int, eps: float, out: torch.Tensor
+) -> torch.Tensor:
+    rows = o.shape[0]
+    _need(o.dtype == torch.float32 and o.is_contiguous() and tuple(out.shape) == (rows, heads * dv) and out.is_contiguous(), "delta_output: bad operands")
+    _need(gate.stride(1) == 1 and gate.shape[1] == heads * dv and gate.dtype == out.dtype, "delta_output: bad gate")
+    _need(weight.dtype == torch.float32 and weight.numel() == dv, "delta_output: weight must be float32 [dv]")
+    ctx.lib.call(
+        "b200_delta_output", ptr(o), ptr(weight), ptr(gate), c_int(gate.stride(0)), c_int(rows), c_int(heads), c_int(dv),
+        c_float(eps), ptr(out), c_int(dtype_code(out.dtype)), ctx.stream,
+    )
+    return out

@@ -16,8 +16,11 @@ class RotaryEncoding(Part):
     tabulated once in 32-bit and the kernel multiplies them by the position
     (python/instinct/backends/portable.py:115-132)."""
 
-    def __init__(self, *, head_dim: int, theta: float, rotary_dims: int | None = None) -> None:
+    def __init__(self, *, head_dim: int, theta: float, rotary_dims: int | None = None, interleaved: bool = False) -> None:
         self.head_dim = head_dim
+        # interleaved: dim 2i pairs with dim 2i + 1 instead of i with i + rotary_dims / 2. The
+        # frequencies are the same; the mixer that owns the part calls the kernel of its layout.
+        self.interleaved = bool(interleaved)
         self.rotary_dims = head_dim if rotary_dims is None else rotary_dims
         if self.rotary_dims % 2 or not 0 <= self.rotary_dims <= head_dim:
             raise ValueError(f"rotary_dims={self.rotary_dims} must be even and at most head_dim={head_dim}")
@@ -48,7 +51,21 @@ class RotaryEncoding(Part):
         the bias, encode each token's position into its queries and keys, store keys and values
         in the token's page of ``cache`` (unless ``cache.writes`` is false) and the queries
         densely in ``q_out``. Here all of it is one kernel."""
+        if self.interleaved:
+            raise ValueError("the fused q/k/v kernel pairs dim i with i + rotary_dims / 2; this part is interleaved")
         return ops.rope_kv_write(ctx, cache, qkv, bias, self.inv_freq, q_out, q_heads, kv_heads, head_dim)
+
+
+    def apply_latent(self, ctx: StepContext, cache: CacheView, proj: torch.Tensor, q_offset: int, kv_offset: int, heads: int,
+                     dim: int, rank: int, norm_weight: torch.Tensor, eps: float, q_rot: torch.Tensor) -> None:
+        """The same duty towards a mixer that caches one latent row per token: ``proj`` holds, per
+        token, ``heads`` queries ``[dim plain | head_dim rotated]`` from column ``q_offset`` and
+        ``[rank latent | head_dim rotated key part]`` from ``kv_offset``. One kernel rotates the query
+        parts into ``q_rot``, RMS-norms the latent (``norm_weight``, ``eps``), rotates the key part
+        and writes both to the token's cache row. Here ``head_dim`` is the size of the rotated part."""
+        if not self.interleaved:
+            raise ValueError("the latent kernel rotates interleaved pairs")
+        ops.latent_kv_write(ctx, cache, proj, q_offset, kv_offset, heads, dim, self.head_dim, rank, norm_weight, eps, self.inv_freq, q_rot)
 
 
 register_part("position", "rotary", RotaryEncoding)

@@ -75,6 +75,11 @@ class TensorSpec:
     # An optional tensor may be absent (a tied output head, for instance).
     optional: bool = False
 
+    def fits(self, shape: tuple[int, ...]) -> bool:
+        """Whether a stored shape is this spec's; a dimension given as -1 (an inner rank that only
+        the checkpoint knows) takes any size."""
+        return len(shape) == len(self.shape) and all(want in (-1, got) for want, got in zip(self.shape, shape))
+
 
 def checkpoint_files(folder: str | Path) -> list[Path]:
     files = sorted(Path(folder).glob("*.safetensors"))
@@ -111,7 +116,7 @@ def load_weights(
                 continue
             file, stored = where[name]
             info = file.tensors[stored]
-            if info.shape != tuple(spec.shape):
+            if not spec.fits(tuple(info.shape)):
                 wrong_shape.append((name, info.shape, tuple(spec.shape)))
             if info.dtype.is_floating_point == spec.integer:
                 wrong_kind.append((name, str(info.dtype).removeprefix("torch.")))

@@ -35,12 +35,16 @@ def random_tensor(
 ) -> torch.Tensor:
     generator = torch.Generator(device=device)
     generator.manual_seed(_stream_seed(seed, spec.name))
+    if any(size < 0 for size in spec.shape):
+        raise ValueError(f"tensor '{spec.name}' has a size that only a checkpoint gives; the configuration must name it to draw weights")
     if spec.integer:
         return torch.zeros(spec.shape, dtype=torch.int32, device=device)
     values = torch.empty(spec.shape, dtype=torch.float32, device=device)
     values.normal_(0.0, std, generator=generator)
     if spec.init == "one_plus_normal":
         values += 1.0
+    elif spec.init == "half_plus_normal":  # positive mixing weights and the like
+        values += 0.5
     elif spec.init != "normal":
         raise ValueError(f"unknown init {spec.init!r} for tensor '{spec.name}'")
     return values.to(dtype)

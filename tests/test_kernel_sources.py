@@ -19,6 +19,8 @@ KERNELS = Path(__file__).resolve().parent.parent / "llm-inference_b200" / "csrc"
 # starts, never by a kernel of the chain.
 BEFORE_THE_CHAIN = {
     "W", "table", "weight", "bias", "inv_freq", "positions", "token_seq", "seq_kv_len", "block_table",
+    # weights and constants of the post-norm blocks, the latent attention and the delta rule
+    "scale", "mix", "coefficients", "norm_weight", "sink", "taps_w", "a_log", "dt_bias",
 }
 
 

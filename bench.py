@@ -263,6 +263,165 @@ def reference_arm(args) -> int:
     return 0
 
 
+# --- the Gunedra design beside the Qwen2 shape of equal size ------------------------------------------------
+
+DESIGN_SIZES = {  # width -> (heads, feed-forward width): the Qwen2.5 1.5B / 7B / 14B layer sizes
+    1536: (12, 8960), 3584: (28, 18944), 5120: (40, 13824),
+}
+DESIGN_LAYERS = 4  # three attention layers and one recurrent layer (or four attention layers of Qwen2)
+DESIGN_VOCAB = 32768
+
+
+def gunedra_shape(width: int) -> dict:
+    """Layer sizes in the proportions of a real model of this design: keys of 128 plain and 64
+    rotated dims, values of 128, a latent of 512; recurrent heads of 128 x 128 with four taps."""
+    heads, ff = DESIGN_SIZES[width]
+    attention = {
+        "type": "latent_attention", "mlp": {"kind": "dense", "ff": ff},
+        "mixer": {"heads": heads, "dim": 128, "rot_dim": 64, "vdim": 128, "kv_rank": 512, "scale": 192 ** -0.5,
+                  "rot": {"base": 1e6, "dims": 64}},
+    }
+    recurrent = {
+        "type": "channel_delta", "mlp": {"kind": "dense", "ff": ff},
+        "mixer": {"heads": heads, "kv_heads": heads, "dim": 128, "vdim": 128, "conv": 4, "decay_rank": 64, "gate_rank": 64},
+    }
+    return {
+        "architecture": "Gunedra", "vocab": DESIGN_VOCAB, "width": width, "residual_mult": 0.7, "embedding": {"scale": width ** 0.5},
+        "norm": {"eps": 1e-5, "groups": 4}, "layers": [attention, attention, recurrent, attention][:DESIGN_LAYERS],
+    }
+
+
+def qwen2_shape(width: int) -> dict:
+    heads, ff = DESIGN_SIZES[width]
+    return dict(MODEL, num_hidden_layers=DESIGN_LAYERS, hidden_size=width, num_attention_heads=heads,
+                num_key_value_heads=max(1, heads // 6), intermediate_size=ff, vocab_size=DESIGN_VOCAB, max_window_layers=DESIGN_LAYERS, eos_token_id=2)
+
+
+def compare_designs(args) -> int:
+    """Prefill of one 2,048-token prompt and decode steps of ``--batch`` requests that hold 2,048
+    tokens, for both designs at each width, device-timed (median of 5 and of 20 after warm-up;
+    every step reads weights far larger than L2 at these sizes only from 3,584 on, so L2 is
+    flushed between timed steps); then one prefill and one decode step with an event pair
+    around every launch of this repository's kernels (overlap between neighbours off), which
+    gives each kernel's time; the rest of the step is the vendor library's matrix products."""
+    import numpy as np
+    import torch
+
+    from llm_inference_b200 import models  # noqa: F401
+    from llm_inference_b200.config import parse_config
+    from llm_inference_b200.engine.engine import Engine
+    from llm_inference_b200.engine.loading import random_model
+    from llm_inference_b200.engine.runner import StepEntry
+
+    if not torch.cuda.is_available():
+        print("bench.py: no CUDA device is visible", file=sys.stderr)
+        return 1
+    torch.cuda.set_device(0)
+    peak = peaks()
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda:0")
+    batch = args.batch
+    results = {}
+    for width in [int(w) for w in args.design_sizes.split(",")]:
+        for design, raw in (("gunedra", gunedra_shape(width)), ("qwen2", qwen2_shape(width))):
+            _, config = parse_config(raw)
+            model = random_model(config, seed=0, dtype="bfloat16", device="cuda:0")
+            engine = Engine(model=model, max_num_sequences=max(batch, 8), max_model_length=CONTEXT, num_pages=(batch + 2) * CONTEXT // PAGE,
+                            page_size=PAGE, prefill_chunk_size=PROMPT, prefill_burst_size=PROMPT, max_batch_tokens=PROMPT + batch)
+            runner, cache, lib = engine.runner, engine.cache, engine.runner.lib
+            rng = np.random.default_rng(0)
+            prompt = [int(t) for t in rng.integers(0, DESIGN_VOCAB, PROMPT)]
+            next_id = [1000]
+
+            def prefill_once() -> None:
+                next_id[0] += 1
+                cache.open(next_id[0])
+                runner.step([StepEntry(next_id[0], prompt, (PROMPT - 1,))])
+                cache.manager.release(next_id[0])
+
+            def timed(fn, repeat: int) -> float:
+                times = []
+                for _ in range(repeat):
+                    flush.zero_()
+                    torch.cuda.synchronize()
+                    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    start.record()
+                    fn()
+                    end.record()
+                    torch.cuda.synchronize()
+                    times.append(start.elapsed_time(end))
+                return statistics.median(times)
+
+            def breakdown(fn) -> dict:
+                """Milliseconds per kernel name of one call of ``fn``, and the whole call's."""
+                records, original = [], lib.call
+
+                def recording(name, *call_args):
+                    first, last = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    first.record()
+                    original(name, *call_args)
+                    last.record()
+                    records.append((name, first, last))
+
+                lib.lib.b200_set_overlap(0)
+                lib.call = recording
+                try:
+                    torch.cuda.synchronize()
+                    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    start.record()
+                    fn()
+                    end.record()
+                    torch.cuda.synchronize()
+                finally:
+                    lib.call = original
+                    lib.lib.b200_set_overlap(1)
+                out: dict = {}
+                for name, first, last in records:
+                    entry = out.setdefault(name.removeprefix("b200_"), {"launches": 0, "ms": 0.0})
+                    entry["launches"] += 1
+                    entry["ms"] += first.elapsed_time(last)
+                own = sum(e["ms"] for e in out.values())
+                out["library products and gaps"] = {"launches": None, "ms": start.elapsed_time(end) - own}
+                return {k: {"launches": v["launches"], "ms": round(v["ms"], 4)} for k, v in out.items()}
+
+            for _ in range(3):
+                prefill_once()
+            prefill_ms = timed(prefill_once, 5)
+            prefill_kernels = breakdown(prefill_once)
+            ids = list(range(1, batch + 1))
+            for rid in ids:
+                cache.open(rid)
+                runner.step([StepEntry(rid, prompt)])
+            feed = rng.integers(0, DESIGN_VOCAB, size=(64, batch))
+            step_at = [0]
+
+            def decode_once() -> None:
+                runner.step([StepEntry(rid, (int(feed[step_at[0] % 64, j]),), (0,)) for j, rid in enumerate(ids)])
+                step_at[0] += 1
+
+            for _ in range(max(3, args.warmup)):
+                decode_once()
+            decode_ms = timed(decode_once, 20)
+            runner.use_graphs = False
+            decode_kernels = breakdown(decode_once)
+            runner.check()
+            weight_bytes = model.weight_bytes()
+            results[f"{design}_{width}"] = {
+                "layers": DESIGN_LAYERS, "weight_bytes": weight_bytes, "cache_bytes_per_token": sum(g.bytes_per_token(2) for g in cache.groups),
+                "prefill_ms": round(prefill_ms, 3), "prefill_tokens_per_s": round(PROMPT / prefill_ms * 1e3),
+                "decode_ms_per_step": round(decode_ms, 4), "decode_tokens_per_s": round(batch / decode_ms * 1e3),
+                "decode_weight_stream_frac_of_hbm": round(weight_bytes / (decode_ms / 1e3) / 1e9 / peak["hbm_gbs"], 3),
+                "prefill_kernels": prefill_kernels, "decode_kernels": decode_kernels,
+            }
+            engine.close()
+            del engine, runner, cache, model
+            torch.cuda.empty_cache()
+    print(json.dumps({
+        "designs": results, "batch": batch, "prompt_len": PROMPT, "dtype": "bf16", "peaks": peak,
+        "data": "synthetic: seeded random weights N(0,0.02), token ids uniform in the vocabulary",
+    }))
+    return 0
+
+
 MIN_TIMED_S = 0.5  # a timed region shorter than this is repeated (and the median pass reported)
 MAX_PASSES = 40
 
@@ -297,9 +456,15 @@ def main() -> int:
     parser.add_argument("--fold-norms", action="store_true", help="fold the norms of short steps into the products around them")
     parser.add_argument("--decode-kernel", choices=["chain", "resident"], default="chain",
                         help="'resident': time the one-kernel decode step instead of the chain of kernels")
+    parser.add_argument("--designs", action="store_true",
+                        help="instead of the headline run: prefill and decode of the Gunedra design beside the Qwen2 shape of "
+                        "equal width, feed-forward and head count, at a few layer sizes, with each kernel's time")
+    parser.add_argument("--design-sizes", default="1536,3584", help="widths for --designs (1536, 3584 or 5120)")
     args = parser.parse_args()
     if args.impl == "reference":
         return reference_arm(args)
+    if args.designs:
+        return compare_designs(args)
     if args.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
         return 2

@@ -78,6 +78,9 @@ _SIGNATURES: dict[str, list] = {
                              c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p],
     "b200_latent_attention_plain": [c_void_p, c_int64, c_int64] + [c_void_p] * 5 + [c_int, c_int, c_void_p, c_void_p, c_int64,
                                     c_void_p, c_int64, c_int64] + [c_int] * 6 + [c_float, c_int, c_void_p, c_void_p],
+    "b200_latent_attention_mma": [c_void_p, c_int64, c_int64, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int] + [c_void_p] * 3
+                                 + [c_int, c_int, c_int, c_void_p, c_void_p, c_int64, c_void_p, c_int64, c_int64, c_int, c_int, c_int,
+                                    c_float, c_int, c_void_p, c_void_p, c_void_p],
     "b200_delta_prepare": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int] + [c_void_p] * 7 + [c_int] * 6 + [c_void_p] * 5
                           + [c_int, c_void_p],
     "b200_delta_recurrence": [c_void_p] * 8 + [c_int] * 5 + [c_void_p] * 3,
@@ -110,6 +113,10 @@ class KernelLibrary:
         self.lib.b200_stream_gemm_trace_stamps.argtypes = []
         self.lib.b200_stream_gemm_trace_stamps.restype = c_int
         self.lib.b200_sm_count.restype = c_int
+        self.lib.b200_latent_attention_mma_supported.argtypes = [c_int] * 4
+        self.lib.b200_latent_attention_mma_supported.restype = c_int
+        self.lib.b200_latent_attention_mma_scratch.argtypes = [c_int] * 5
+        self.lib.b200_latent_attention_mma_scratch.restype = c_int64
         self.lib.b200_skinny_gemm_fold_parts.argtypes = [c_int, c_int]
         self.lib.b200_skinny_gemm_fold_parts.restype = c_int
         self.lib.b200_stream_gemm_fold_parts.argtypes = [c_int, c_int, c_int]

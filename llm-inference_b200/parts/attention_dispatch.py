@@ -79,6 +79,28 @@ def attend_latent(
     rot_dim: int,
     scale: float,
 ) -> None:
-    """Attention over cached latents (parts/latent_attention.py): the plain kernel, which takes
-    float32 and every shape."""
-    ops.latent_attention_plain(ctx, cache, q_lat, q_rot, sink, gate, out, heads, rank, rot_dim, scale)
+    """Attention over cached latents (parts/latent_attention.py). bfloat16 with a shape the
+    tensor-core kernel takes: the step's single-token requests (which lead the batch) in one
+    launch whose blocks cut every request's keys into pieces, merged by a second kernel; the
+    prompt portions in another, one block per 64 (token, head) rows. float32 and every other
+    shape: the plain kernel. ``options["attention"]``: ``"plain"`` forces the plain kernel,
+    ``"flash"`` refuses what the tensor-core kernel does not take; ``options["latent_pieces"]``
+    forces the number of pieces."""
+    choice = ctx.options.get("attention", "auto")
+    tuned = (
+        choice != "plain" and q_lat.dtype == torch.bfloat16 and not cache.window
+        and ops.latent_attention_mma_supported(ctx, heads, rank, rot_dim, cache.page_size)
+    )
+    if not tuned:
+        if choice == "flash":
+            raise ops.KernelError("the tensor-core latent attention kernel does not take this shape or dtype")
+        ops.latent_attention_plain(ctx, cache, q_lat, q_rot, sink, gate, out, heads, rank, rot_dim, scale)
+        return
+    decode_seqs = ctx.num_decode_seqs
+    if decode_seqs:
+        pieces = int(ctx.options.get("latent_pieces", 0)) or ops.latent_attention_pieces(decode_seqs, heads, ctx.max_kv_len, ops.sm_count(ctx))
+        ops.latent_attention_mma(ctx, cache, q_lat, q_rot, sink, gate, out, heads, rank, rot_dim, scale,
+                                 first_seq=0, num_seqs=decode_seqs, max_q_len=1, pieces=pieces)
+    if ctx.num_seqs > decode_seqs:
+        ops.latent_attention_mma(ctx, cache, q_lat, q_rot, sink, gate, out, heads, rank, rot_dim, scale,
+                                 first_seq=decode_seqs, num_seqs=ctx.num_seqs - decode_seqs, max_q_len=ctx.max_q_len)

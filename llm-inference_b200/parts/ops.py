@@ -692,6 +692,49 @@ def latent_attention_plain(
     return out
 
 
+def latent_attention_mma_supported(ctx: StepContext, heads: int, rank: int, rot_dim: int, page_size: int) -> bool:
+    return bool(ctx.lib.lib.b200_latent_attention_mma_supported(heads, rank, rot_dim, page_size))
+
+
+def latent_attention_pieces(num_seqs: int, heads: int, max_kv_len: int, num_sms: int = NUM_SMS) -> int:
+    """Into how many pieces a step of single tokens cuts each request's keys: enough blocks for two
+    per SM, every piece at least two tiles of 32 keys, at most 64 pieces."""
+    rows_per_block = 16 if heads <= 16 else (32 if heads <= 32 else 64)
+    blocks = max(1, num_seqs * ((heads + rows_per_block - 1) // rows_per_block))
+    tiles = max(1, (max_kv_len + 31) // 32)
+    return max(1, min(2 * num_sms // blocks, tiles // 2, 64))
+
+
+def latent_attention_mma(
+    ctx: StepContext, cache: CacheView, q_lat: torch.Tensor, q_rot: torch.Tensor, sink: torch.Tensor | None,
+    gate: torch.Tensor | None, out: torch.Tensor, heads: int, rank: int, rot_dim: int, scale: float, *,
+    first_seq: int, num_seqs: int, max_q_len: int, pieces: int = 1,
+) -> torch.Tensor:
+    """The tensor-core kernel (bfloat16) for requests ``first_seq .. first_seq + num_seqs`` of the step; operands as
+    for :func:`latent_attention_plain`. With ``pieces`` > 1 every request's keys are cut and merged through scratch."""
+    if num_seqs <= 0:
+        return out
+    tokens = q_rot.shape[0]
+    _need(q_lat.dtype == torch.bfloat16 and out.dtype == torch.bfloat16 and cache.keys.dtype == torch.bfloat16, "latent attention (tensor cores) is bfloat16 only")
+    _need(tuple(q_lat.shape) == (heads, tokens, rank) and q_lat.stride(2) == 1 and tuple(out.shape) == (heads, tokens, rank) and out.stride(2) == 1, "latent attention: bad operands")
+    _need(q_rot.is_contiguous() and cache.window == 0, "latent attention (tensor cores): dense rotated queries, no window")
+    _need(gate is None or (tuple(gate.shape) == (tokens, heads) and gate.stride(1) == 1 and gate.dtype == torch.bfloat16), "latent attention: bad gate")
+    scratch = None
+    if pieces > 1:
+        floats = int(ctx.lib.lib.b200_latent_attention_mma_scratch(num_seqs, max_q_len, heads, rank, pieces))
+        scratch = ctx.buffer("latent_partials", (floats,), torch.float32, per_token=False)
+    ctx.lib.call(
+        "b200_latent_attention_mma", ptr(q_lat), c_int64(q_lat.stride(1)), c_int64(q_lat.stride(0)), ptr(q_rot), ptr(cache.keys),
+        ptr(cache.block_table), c_int(cache.max_pages), c_int(cache.num_pages), c_int(cache.page_size), ptr(ctx.seq_q_start),
+        ptr(ctx.seq_q_len), ptr(ctx.seq_kv_len), c_int(first_seq), c_int(num_seqs), c_int(max_q_len), ptr(sink), ptr(gate),
+        c_int64(gate.stride(0) if gate is not None else 0), ptr(out), c_int64(out.stride(1)), c_int64(out.stride(0)), c_int(heads),
+        c_int(rank), c_int(rot_dim), c_float(scale), c_int(pieces), ptr(scratch), ptr(ctx.err), ctx.stream,
+    )
+    if scratch is not None:
+        ctx.lib.calls += 1  # the merge kernel is a launch of its own
+    return out
+
+
 # -- the gated delta rule -----------------------------------------------------------------------------------
 
 

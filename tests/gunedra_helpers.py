@@ -60,7 +60,18 @@ BETA = config_of(
     ],
     mult=1.3, embedding_scale=0.7, eps=3e-4,
 )
-CONFIGS = {"alpha": ALPHA, "beta": BETA}
+# GAMMA: latents whose sizes the tensor-core attention kernel takes in bfloat16 (a multiple of 32 with a
+# rotated part of a multiple of 16), with 3 and 5 heads so that a block's rows straddle tokens.
+GAMMA = config_of(
+    64, 113, 2,
+    [
+        with_mlp(latent_mixer(heads=3, dim=16, rot_dim=16, vdim=24, kv_rank=64), 96),
+        with_mlp(delta_mixer(heads=2, kv_heads=2, dim=16, vdim=16, conv=4, decay_rank=4, gate_rank=4), 64),
+        with_mlp(latent_mixer(heads=5, dim=8, rot_dim=32, vdim=8, kv_rank=160, rot_dims=32, base=2e4), 80),
+    ],
+    mult=0.8, embedding_scale=4.0,
+)
+CONFIGS = {"alpha": ALPHA, "beta": BETA, "gamma": GAMMA}
 
 
 def draw_weights(config: dict, seed: int, sharp: float = 4.0) -> dict[str, torch.Tensor]:

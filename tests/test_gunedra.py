@@ -208,13 +208,68 @@ def test_delta_rule_alone_in_portions_beside_another_request(name, sizes):
     np.testing.assert_allclose(np.concatenate(got[11]), want[11], **tolerance)
 
 
+@pytest.mark.parametrize("heads,rank,rot_dim", [(3, 64, 16), (5, 160, 32), (6, 128, 32), (12, 512, 64), (40, 96, 16), (1, 32, 0)])
+def test_tensor_core_latent_attention_against_the_plain_kernel(heads, rank, rot_dim):
+    """bfloat16: three single tokens (a request's very first token, one at a page border, one far in)
+    and three prompt portions (from the start, deep in a request, across many pages) in one step; the
+    pages hold NaN wherever the requests have not written, queries are sharp, sinks and gates matter.
+    The keys of single tokens are cut into 1, 3 and the default number of pieces."""
+    from llm_inference_b200.parts import ops
+    from llm_inference_b200.parts.base import KVCacheSpec
+
+    from llm_inference_b200.engine.runner import StepEntry
+
+    runs, starts = [1, 1, 1, 37, 5, 70], [0, 63, 150, 0, 90, 31]
+    runner, cache, _ = context_for({0: KVCacheSpec(1, rank + rot_dim, 0, planes=1)}, torch.bfloat16, [1])
+    entries = []
+    for i, (run, start) in enumerate(zip(runs, starts)):
+        cache.open(10 + i)
+        cache.manager.ensure(10 + i, start + run)
+        cache.manager.advance(10 + i, start)
+        entries.append(StepEntry(10 + i, [0] * run))
+    ctx = runner._build_context(entries, starts, [])
+    assert ops.latent_attention_mma_supported(ctx, heads, rank, rot_dim, cache.page_size) and ctx.num_decode_seqs == 3
+    view = cache.view(0, True, runner._tables)
+    generator = torch.Generator(device="cuda").manual_seed(heads * 1000 + rank)
+    normal = lambda *shape: torch.randn(*shape, device="cuda", generator=generator)
+    view.keys.fill_(float("nan"))
+    table = runner._tables[0].cpu().numpy()
+    for i, (run, start) in enumerate(zip(runs, starts)):
+        for j in range(start + run):
+            view.keys[int(table[i, j // 8]), 0, j % 8] = normal(rank + rot_dim).to(torch.bfloat16)
+    tokens = sum(runs)
+    q_lat = (normal(heads, tokens, rank) * 3.0 / rank**0.5).to(torch.bfloat16)
+    q_rot = (normal(tokens, heads * rot_dim) * 0.5).to(torch.bfloat16)
+    sink = normal(heads) + 1.5
+    gate = normal(tokens, heads + 3).to(torch.bfloat16)[:, 1 : heads + 1]  # a slice of wider rows, as in the mixer
+    want = torch.empty(heads, tokens, rank, dtype=torch.bfloat16, device="cuda")
+    ops.latent_attention_plain(ctx, view, q_lat, q_rot, sink, gate, want, heads, rank, rot_dim, 0.9)
+    assert torch.isfinite(want).all() and want.float().std() > 0.05
+    for pieces in (1, 3, 0):
+        got = torch.full_like(want, float("nan"))
+        if pieces:
+            ops.latent_attention_mma(ctx, view, q_lat, q_rot, sink, gate, got, heads, rank, rot_dim, 0.9, first_seq=0, num_seqs=3, max_q_len=1, pieces=pieces)
+            ops.latent_attention_mma(ctx, view, q_lat, q_rot, sink, gate, got, heads, rank, rot_dim, 0.9, first_seq=3, num_seqs=3, max_q_len=70)
+        else:
+            from llm_inference_b200.parts import attention_dispatch
+
+            attention_dispatch.attend_latent(ctx, view, q_lat, q_rot, sink, gate, got, heads, rank, rot_dim, 0.9)
+        runner.check()
+        np.testing.assert_allclose(got.float().cpu().numpy(), want.float().cpu().numpy(), atol=2e-2, rtol=2e-2, err_msg=f"pieces {pieces}")
+    # without sink and gate
+    ops.latent_attention_plain(ctx, view, q_lat, q_rot, None, None, want, heads, rank, rot_dim, 0.9)
+    got = torch.full_like(want, float("nan"))
+    ops.latent_attention_mma(ctx, view, q_lat, q_rot, None, None, got, heads, rank, rot_dim, 0.9, first_seq=0, num_seqs=6, max_q_len=70)
+    np.testing.assert_allclose(got.float().cpu().numpy(), want.float().cpu().numpy(), atol=2e-2, rtol=2e-2)
+
+
 # --- whole models ---------------------------------------------------------------------------------------------
 
 
 LENGTHS = [1, 2, 3, 9, 31, 70, 150]
 
 
-@pytest.fixture(scope="module", params=["alpha", "beta"])
+@pytest.fixture(scope="module", params=["alpha", "beta", "gamma"])
 def model_case(request, tmp_path_factory):
     config = CONFIGS[request.param]
     weights = draw_weights(config, seed=17 + len(request.param))

@@ -90,79 +90,130 @@ __global__ void conv_state_update_kernel(const T* proj, int ld, int channels, in
   }
 }
 
-// A block owns kCols columns of one head of one request; a column's dk rows are spread over
+// A block owns `cols` columns of one head of one request; a column's dk rows are spread over
 // `lanes_per_col` neighbouring lanes (row r on lane r % lanes_per_col), PER rows per lane in
-// registers. The block stages kStage tokens' q, k, g, v and beta in shared memory at a time.
+// registers: few rows per lane keep the two dot products' chains of dependent FMAs short, which
+// is what a token's latency is made of. The tokens' q, k, g, v and beta arrive kStage at a time
+// by cp.async in a ring of two stages, so the next tokens load while these are worked on.
 constexpr int kRecurrenceThreads = 128;
 constexpr int kStage = 8;
 
-template <int PER>
+// `bytes` (4 or 16) global -> shared; with `valid` false zeros are written and nothing is read.
+template <int kBytes>
+__device__ __forceinline__ void stage_copy(float* smem, const float* gmem, bool valid) {
+  const uint32_t s = static_cast<uint32_t>(__cvta_generic_to_shared(smem));
+  const int bytes = valid ? kBytes : 0;
+  asm volatile("cp.async.ca.shared.global [%0], [%1], %2, %3;" ::"r"(s), "l"(gmem), "n"(kBytes), "r"(bytes) : "memory");
+}
+
+template <int PER, int LANES>
 __global__ void __launch_bounds__(kRecurrenceThreads)
 delta_recurrence_kernel(const float* q, const float* k, const float* v, const float* beta, const float* decay,
                         const int* seq_q_start, const int* seq_q_len, const int* seq_slot, int heads, int kv_heads, int dk,
-                        int dv, int lanes_per_col, float* state, float* out) {
-  extern __shared__ float stage[];
-  wait_for_predecessor();
+                        int dv, int vec, float* state, float* out) {
+  extern __shared__ __align__(16) float stage[];
   let_successor_start();
-  const int cols = kRecurrenceThreads / lanes_per_col;
+  constexpr int lanes_per_col = LANES;
+  constexpr int cols = kRecurrenceThreads / lanes_per_col;
   const int seq = blockIdx.x, head = blockIdx.y, col0 = blockIdx.z * cols;
   const int tid = threadIdx.x;
   const int part = tid % lanes_per_col, col = col0 + tid / lanes_per_col;
-  const int padded = PER * lanes_per_col;
-  float* sq = stage;                       // [kStage][padded]
-  float* sk = sq + kStage * padded;        // [kStage][padded]
-  float* sg = sk + kStage * padded;        // [kStage][padded]
-  float* sv = sg + kStage * padded;        // [kStage][cols]
-  float* sb = sv + kStage * cols;          // [kStage]
+  constexpr int padded = PER * lanes_per_col;
+  constexpr int per_stage = kStage * (3 * padded + cols) + kStage;
   const int start = seq_q_start[seq], len = seq_q_len[seq];
   const int kvh = head / (heads / kv_heads);
   const bool live = col < dv;
   float* s_base = state + (static_cast<int64_t>(seq_slot[seq]) * heads + head) * dk * dv;
+  wait_for_predecessor();
+  // Rows past dk (when dk is no multiple of the lanes) hold zeros in q, k and g and stay zero.
+  auto fetch = [&](int buffer, int t0) {
+    float* sq = stage + buffer * per_stage;
+    float* sk = sq + kStage * padded;
+    float* sg = sk + kStage * padded;
+    float* sv = sg + kStage * padded;
+    float* sb = sv + kStage * cols;
+    const int count = min(kStage, len - t0);
+    const int64_t first = static_cast<int64_t>(start) + t0;
+    if (vec) {
+      for (int idx = tid * 4; idx < count * padded; idx += kRecurrenceThreads * 4) {
+        const int j = idx / padded, r = idx % padded;
+        const int64_t tok = first + j;
+        const bool in = r < dk;
+        const int rr = in ? r : 0;
+        stage_copy<16>(sq + idx, q + (tok * kv_heads + kvh) * dk + rr, in);
+        stage_copy<16>(sk + idx, k + (tok * kv_heads + kvh) * dk + rr, in);
+        stage_copy<16>(sg + idx, decay + (tok * heads + head) * dk + rr, in);
+      }
+      for (int idx = tid * 4; idx < count * cols; idx += kRecurrenceThreads * 4) {
+        const int j = idx / cols, c = col0 + idx % cols;
+        stage_copy<16>(sv + idx, v + ((first + j) * heads + head) * dv + (c < dv ? c : 0), c < dv);
+      }
+    } else {
+      for (int idx = tid; idx < count * padded; idx += kRecurrenceThreads) {
+        const int j = idx / padded, r = idx % padded;
+        const int64_t tok = first + j;
+        const bool in = r < dk;
+        const int rr = in ? r : 0;
+        stage_copy<4>(sq + idx, q + (tok * kv_heads + kvh) * dk + rr, in);
+        stage_copy<4>(sk + idx, k + (tok * kv_heads + kvh) * dk + rr, in);
+        stage_copy<4>(sg + idx, decay + (tok * heads + head) * dk + rr, in);
+      }
+      for (int idx = tid; idx < count * cols; idx += kRecurrenceThreads) {
+        const int j = idx / cols, c = col0 + idx % cols;
+        stage_copy<4>(sv + idx, v + ((first + j) * heads + head) * dv + (c < dv ? c : 0), c < dv);
+      }
+    }
+    if (tid < count) stage_copy<4>(sb + tid, beta + (first + tid) * heads + head, true);
+  };
   float s[PER];
 #pragma unroll
   for (int i = 0; i < PER; ++i) {
     const int r = i * lanes_per_col + part;
     s[i] = (live && r < dk) ? s_base[static_cast<int64_t>(r) * dv + col] : 0.f;
   }
-  for (int t0 = 0; t0 < len; t0 += kStage) {
+  if (len > 0) fetch(0, 0);
+  asm volatile("cp.async.commit_group;" ::: "memory");
+  for (int t0 = 0, buffer = 0; t0 < len; t0 += kStage, buffer ^= 1) {
+    if (t0 + kStage < len) fetch(buffer ^ 1, t0 + kStage);
+    asm volatile("cp.async.commit_group;" ::: "memory");
+    asm volatile("cp.async.wait_group 1;" ::: "memory");
+    __syncthreads();
+    const float* sq = stage + buffer * per_stage;
+    const float* sk = sq + kStage * padded;
+    const float* sg = sk + kStage * padded;
+    const float* sv = sg + kStage * padded;
+    const float* sb = sv + kStage * cols;
     const int count = min(kStage, len - t0);
-    __syncthreads();
-    for (int idx = tid; idx < count * padded; idx += kRecurrenceThreads) {
-      const int j = idx / padded, r = idx % padded;
-      const int64_t tok = start + t0 + j;
-      const bool in = r < dk;
-      sq[idx] = in ? q[tok * kv_heads * dk + kvh * dk + r] : 0.f;
-      sk[idx] = in ? k[tok * kv_heads * dk + kvh * dk + r] : 0.f;
-      sg[idx] = in ? decay[tok * heads * dk + head * dk + r] : 1.f;
-    }
-    for (int idx = tid; idx < count * cols; idx += kRecurrenceThreads) {
-      const int j = idx / cols, c = col0 + idx % cols;
-      sv[idx] = c < dv ? v[(static_cast<int64_t>(start) + t0 + j) * heads * dv + head * dv + c] : 0.f;
-    }
-    if (tid < count) sb[tid] = beta[(static_cast<int64_t>(start) + t0 + tid) * heads + head];
-    __syncthreads();
     for (int j = 0; j < count; ++j) {
       const float* kj = sk + j * padded + part;
       const float* gj = sg + j * padded + part;
       const float* qj = sq + j * padded + part;
-      float ks = 0.f;
+      float kr[PER];
+      float ks0 = 0.f, ks1 = 0.f;
 #pragma unroll
-      for (int i = 0; i < PER; ++i) {
-        s[i] *= gj[i * lanes_per_col];
-        ks = fmaf(kj[i * lanes_per_col], s[i], ks);
+      for (int i = 0; i < PER; i += 2) {
+        kr[i] = kj[i * lanes_per_col], kr[i + 1] = kj[(i + 1) * lanes_per_col];
+        s[i] *= gj[i * lanes_per_col], s[i + 1] *= gj[(i + 1) * lanes_per_col];
+        ks0 = fmaf(kr[i], s[i], ks0), ks1 = fmaf(kr[i + 1], s[i + 1], ks1);
       }
+      float ks = ks0 + ks1;
+#pragma unroll
       for (int o = lanes_per_col >> 1; o > 0; o >>= 1) ks += __shfl_xor_sync(0xffffffffu, ks, o);
       const float u = sb[j] * (sv[j * cols + tid / lanes_per_col] - ks);
-      float qs = 0.f;
+      float qs0 = 0.f, qs1 = 0.f;
 #pragma unroll
-      for (int i = 0; i < PER; ++i) {
-        s[i] = fmaf(kj[i * lanes_per_col], u, s[i]);
-        qs = fmaf(qj[i * lanes_per_col], s[i], qs);
+      for (int i = 0; i < PER; i += 2) {
+        s[i] = fmaf(kr[i], u, s[i]), s[i + 1] = fmaf(kr[i + 1], u, s[i + 1]);
+        qs0 = fmaf(qj[i * lanes_per_col], s[i], qs0), qs1 = fmaf(qj[(i + 1) * lanes_per_col], s[i + 1], qs1);
       }
+      float qs = qs0 + qs1;
+#pragma unroll
       for (int o = lanes_per_col >> 1; o > 0; o >>= 1) qs += __shfl_xor_sync(0xffffffffu, qs, o);
       if (live && part == 0) out[(static_cast<int64_t>(start) + t0 + j) * heads * dv + head * dv + col] = qs;
     }
+    __syncthreads();
   }
+  asm volatile("cp.async.wait_group 0;" ::: "memory");
 #pragma unroll
   for (int i = 0; i < PER; ++i) {
     const int r = i * lanes_per_col + part;
@@ -238,23 +289,34 @@ B200_API int b200_delta_recurrence(const float* q, const float* k, const float* 
   B200_REQUIRE(seqs > 0 && heads > 0 && heads <= 65535 && kv_heads > 0 && heads % kv_heads == 0 && dk > 0 && dv > 0,
                "delta_recurrence: bad sizes");
   B200_REQUIRE(dk <= 1024, "delta_recurrence: %d key channels per head, at most 1024", dk);
-  // As few lanes per column as keep a lane's rows in registers (32 at most).
+  // Lanes per column: enough that a lane holds at most 8 rows (up to 32 rows when even a whole warp
+  // per column leaves more).
   int lanes = 1;
-  while ((dk + lanes - 1) / lanes > 32) lanes *= 2;
+  while ((dk + lanes - 1) / lanes > 8 && lanes < 32) lanes *= 2;
   const int rows = (dk + lanes - 1) / lanes;
-  const int per = rows <= 4 ? 4 : (rows <= 8 ? 8 : (rows <= 16 ? 16 : 32));
+  B200_REQUIRE(rows <= 32, "delta_recurrence: %d key channels per head, at most 1024", dk);
+  const int per = rows <= 8 ? 8 : (rows <= 16 ? 16 : 32);
   const int cols = kRecurrenceThreads / lanes;
   const dim3 grid(seqs, heads, (dv + cols - 1) / cols);
   B200_REQUIRE(grid.z <= 65535, "delta_recurrence: too many columns");
-  const size_t smem = sizeof(float) * (kStage * (3 * per * lanes + cols) + kStage);
+  const size_t smem = sizeof(float) * 2 * (kStage * (3 * per * lanes + cols) + kStage);
+  const auto aligned = [](const void* p) { return reinterpret_cast<uintptr_t>(p) % 16 == 0; };
+  // 16-byte copies when every staged row starts on a 16-byte boundary.
+  const int vec = dk % 4 == 0 && dv % 4 == 0 && aligned(q) && aligned(k) && aligned(v) && aligned(decay) ? 1 : 0;
+  B200_REQUIRE(smem <= 200 * 1024, "delta_recurrence: the staged tokens do not fit shared memory");
   auto launch = [&](auto kernel) {
+    if (smem > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
     launch_kernel(kernel, grid, dim3(kRecurrenceThreads), smem, stream, q, k, v, beta, decay, seq_q_start, seq_q_len, seq_slot,
-                  heads, kv_heads, dk, dv, lanes, state, out);
+                  heads, kv_heads, dk, dv, vec, state, out);
   };
-  if (per == 4) launch(delta_recurrence_kernel<4>);
-  else if (per == 8) launch(delta_recurrence_kernel<8>);
-  else if (per == 16) launch(delta_recurrence_kernel<16>);
-  else launch(delta_recurrence_kernel<32>);
+  if (per == 32) launch(delta_recurrence_kernel<32, 32>);
+  else if (per == 16) launch(delta_recurrence_kernel<16, 32>);
+  else if (lanes == 32) launch(delta_recurrence_kernel<8, 32>);
+  else if (lanes == 16) launch(delta_recurrence_kernel<8, 16>);
+  else if (lanes == 8) launch(delta_recurrence_kernel<8, 8>);
+  else if (lanes == 4) launch(delta_recurrence_kernel<8, 4>);
+  else if (lanes == 2) launch(delta_recurrence_kernel<8, 2>);
+  else launch(delta_recurrence_kernel<8, 1>);
   return b200_check_launch("delta_recurrence");
 }
 

@@ -108,24 +108,25 @@ __global__ void __launch_bounds__(64 * RW, 1) latent_attention_mma_kernel(const 
                                             : p.q_rot + (static_cast<int64_t>(token) * p.heads + head) * p.rot_dim + (col - p.rank);
     copy16(qs + r * ld + col, src, valid);
   }
+  // A tile is 32 keys: lane i of every warp looks up the page of key i (one trip to the block table
+  // per tile, not one per copy), the warps share the keys out, a warp's lanes the 16-byte pieces of a row.
   auto load_tile = [&](int stage, int tile) {
     __nv_bfloat16* dst = ks + stage * kKeys * ld;
-    for (int idx = tid; idx < kKeys * chunks; idx += kThreads) {
-      const int key = idx / chunks, col = (idx % chunks) * 8;
-      const int j = tile * kKeys + key;
-      bool valid = j <= max_pos;
-      int page = 0;
-      if (valid) {
-        const int logical = j / p.page_size;
-        page = logical < p.max_pages ? table[logical] : -1;
-        if (page < 0 || page >= p.num_pages) {
-          if (col == 0) atomicOr(p.err, ERRBIT_BAD_PAGE);
-          valid = false;
-          page = 0;
-        }
+    const int mine = tile * kKeys + lane;
+    int64_t my_row = -1;
+    if (mine <= max_pos) {
+      const int logical = mine / p.page_size;
+      const int page = logical < p.max_pages ? table[logical] : -1;
+      if (page < 0 || page >= p.num_pages) {
+        if (warp == 0) atomicOr(p.err, ERRBIT_BAD_PAGE);
+      } else {
+        my_row = static_cast<int64_t>(page) * p.page_size + mine % p.page_size;
       }
-      const __nv_bfloat16* src = p.arena + (static_cast<int64_t>(page) * p.page_size + (valid ? j % p.page_size : 0)) * width + col;
-      copy16(dst + key * ld + col, src, valid);
+    }
+    for (int key = warp; key < kKeys; key += kThreads / 32) {
+      const int64_t row = __shfl_sync(0xffffffffu, my_row, key);
+      const __nv_bfloat16* src = p.arena + (row < 0 ? 0 : row) * width;
+      for (int c = lane; c < chunks; c += 32) copy16(dst + key * ld + c * 8, src + c * 8, row >= 0);
     }
   };
 

@@ -233,6 +233,80 @@ def bench_attention(args, decode: bool) -> dict:
             "layers": args.layers, "us": us, "GBps": kv_bytes / us / 1e3, "TFLOPs": flops / us / 1e6}
 
 
+def bench_latent_attention(args, decode: bool) -> dict:
+    """Attention over cached latents (parts/latent_attention.py): ``--q-heads`` heads over rows of
+    ``--rank`` + ``--rot-dim`` numbers; bytes are the cached rows read once per request, flops the
+    scores and the weighted sums over those rows (2 * (2 rank + rot_dim) per head, query and key)."""
+    from ..parts import attention_dispatch
+    from ..parts.context import CacheView
+
+    heads, rank, rot, page = args.q_heads, args.rank, args.rot_dim, args.page
+    if decode:
+        starts, runs = [args.context - 1] * args.batch, [1] * args.batch
+    else:
+        starts, runs = [args.context - args.tokens], [args.tokens]
+    lens = [s + r for s, r in zip(starts, runs)]
+    need = [-(-n // page) for n in lens]
+    num_pages = sum(need) + 1
+    order = np.random.default_rng(0).permutation(num_pages - 1)
+    tables = np.zeros((len(lens), max(need)), dtype=np.int32)
+    at = 0
+    for s, c in enumerate(need):
+        tables[s, :c] = order[at : at + c]
+        at += c
+    positions = [p for s, r in zip(starts, runs) for p in range(s, s + r)]
+    token_seq = [i for i, r in enumerate(runs) for _ in range(r)]
+    options = {"attention": "plain" if args.plain else "auto"}
+    if args.splits:
+        options["latent_pieces"] = args.splits
+    ctx = make_ctx(positions, token_seq, starts, runs, options)
+    tokens = len(positions)
+    q_lat = (torch.randn(heads, tokens, rank, device="cuda") / rank**0.5).to(torch.bfloat16)
+    q_rot = torch.randn(tokens, heads * rot, device="cuda").to(torch.bfloat16)
+    gate = torch.randn(tokens, heads, device="cuda").to(torch.bfloat16)
+    sink = torch.zeros(heads, device="cuda")
+    out = torch.empty_like(q_lat)
+    table = torch.from_numpy(tables).cuda()
+    fns = []
+    for _ in range(max(1, args.layers)):
+        rows = torch.randn(num_pages, 1, page, rank + rot, device="cuda").to(torch.bfloat16)
+        view = CacheView(0, True, rows, None, table, num_pages, tables.shape[1], page, 0)
+        fns.append(lambda view=view: attention_dispatch.attend_latent(ctx, view, q_lat, q_rot, sink, gate, out, heads, rank, rot, (rank + rot) ** -0.5))
+    us = time_back_to_back(fns, 16 * len(fns)) if args.rotate else time_launches(fns[0], args.iters)
+    row_bytes = sum(lens) * (rank + rot) * 2
+    flops = sum(2.0 * heads * (2 * rank + rot) * r * (s + (r + 1) / 2) for s, r in zip(starts, runs))
+    return {"kernel": "latent_decode_attention" if decode else "latent_prefill_attention", "batch": len(lens), "context": args.context,
+            "tokens": tokens, "heads": heads, "rank": rank, "rot_dim": rot, "pieces": args.splits, "layers": args.layers,
+            "us": us, "GBps": row_bytes / us / 1e3, "TFLOPs": flops / us / 1e6}
+
+
+def bench_delta_recurrence(args) -> dict:
+    """The gated delta rule's recurrence (parts/delta_rule.py) over ``--batch`` requests of
+    ``--tokens`` tokens each: ``--q-heads`` heads with states of ``--head-dim`` x ``--vdim``. Flops:
+    per token and head three products over the state (decay, k-dot and update, q-dot)."""
+    from ..parts import ops
+
+    heads, dk, dv, batch, tokens = args.q_heads, args.head_dim, args.vdim, args.batch, args.tokens
+    runs, starts = [tokens] * batch, [0] * batch
+    positions = [p for r in runs for p in range(r)]
+    token_seq = [i for i, r in enumerate(runs) for _ in range(r)]
+    ctx = make_ctx(positions, token_seq, starts, runs)
+    ctx.seq_slot = torch.arange(batch, dtype=torch.int32, device="cuda")
+    total = batch * tokens
+    unit = lambda x: x / x.norm(dim=-1, keepdim=True)
+    q = unit(torch.randn(total, heads, dk, device="cuda")).reshape(total, heads * dk).contiguous()
+    k = unit(torch.randn(total, heads, dk, device="cuda")).reshape(total, heads * dk).contiguous()
+    v = torch.randn(total, heads * dv, device="cuda")
+    beta = torch.rand(total, heads, device="cuda")
+    decay = torch.rand(total, heads * dk, device="cuda") * 0.2 + 0.8
+    state = torch.zeros(batch, heads, dk, dv, device="cuda")
+    out = torch.empty(total, heads * dv, device="cuda")
+    us = time_launches(lambda: ops.delta_recurrence(ctx, q, k, v, beta, decay, state, out, heads, heads, dk, dv), args.iters)
+    moved = 4.0 * (total * (3 * heads * dk + 2 * heads * dv + heads) + 2 * batch * heads * dk * dv)
+    return {"kernel": "delta_recurrence", "batch": batch, "tokens": tokens, "heads": heads, "dim": dk, "vdim": dv, "us": us,
+            "us_per_token": us / tokens, "GBps": moved / us / 1e3, "TFLOPs": 7.0 * total * heads * dk * dv / us / 1e6}
+
+
 def bench_resident(args) -> dict:
     """One decode step as the resident kernel at a named shape: time per step, and for each kind of
     phase how long the slowest block takes to ask for its operand, to finish, and how long block 0
@@ -346,7 +420,11 @@ def bench_timeline(args) -> dict:
 
 def main(argv=None) -> int:
     parser = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
-    parser.add_argument("kernel", choices=["gemm", "decode_attention", "prefill_attention", "resident", "timeline"])
+    parser.add_argument("kernel", choices=["gemm", "decode_attention", "prefill_attention", "resident", "timeline",
+                                           "latent_decode_attention", "latent_prefill_attention", "delta_recurrence"])
+    parser.add_argument("--rank", type=int, default=512, help="latent attention: size of the cached latent")
+    parser.add_argument("--rot-dim", type=int, default=64, help="latent attention: size of the shared rotated key part")
+    parser.add_argument("--vdim", type=int, default=128, help="delta_recurrence: value size per head")
     parser.add_argument("--shape", default="qwen2.5-1.5b", help="resident, timeline: a named model shape")
     parser.add_argument("--m", type=int, default=8)
     parser.add_argument("--n", type=int, default=17920)
@@ -384,6 +462,10 @@ def main(argv=None) -> int:
         result = bench_resident(args)
     elif args.kernel == "timeline":
         result = bench_timeline(args)
+    elif args.kernel.startswith("latent_"):
+        result = bench_latent_attention(args, args.kernel == "latent_decode_attention")
+    elif args.kernel == "delta_recurrence":
+        result = bench_delta_recurrence(args)
     else:
         result = bench_attention(args, args.kernel == "decode_attention")
     print(json.dumps(result))

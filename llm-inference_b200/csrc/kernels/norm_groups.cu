@@ -126,6 +126,130 @@ __global__ void poly_norm_kernel(const T* z, const float* __restrict__ coefficie
   }
 }
 
+// Four neighbouring values as one access (16 bytes of float, 8 of bfloat16).
+template <typename T>
+struct Four;
+template <>
+struct Four<float> {
+  static __device__ __forceinline__ float4 load(const float* p) { return *reinterpret_cast<const float4*>(p); }
+  static __device__ __forceinline__ void store(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+};
+template <>
+struct Four<__nv_bfloat16> {
+  static __device__ __forceinline__ float4 load(const __nv_bfloat16* p) {
+    const uint2 raw = *reinterpret_cast<const uint2*>(p);
+    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+    const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+    return make_float4(a.x, a.y, b.x, b.y);
+  }
+  static __device__ __forceinline__ void store(__nv_bfloat16* p, float4 v) {
+    const __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+    uint2 raw;
+    raw.x = *reinterpret_cast<const uint32_t*>(&a);
+    raw.y = *reinterpret_cast<const uint32_t*>(&b);
+    *reinterpret_cast<uint2*>(p) = raw;
+  }
+};
+
+constexpr int kFoursPerThread = 4;  // a thread keeps up to this many groups of four of its row in registers
+
+// branch_norm_add with 16-byte accesses: rows whose groups are multiples of four long and fit the
+// registers (hidden <= 16 * threads). The row of the branch output is read once: each thread's
+// sums of squares go to shared memory by position, one warp per norm group adds its range in a
+// fixed order.
+template <typename T>
+__global__ void branch_norm_add_vec_kernel(const float* in_x, const T* delta, const float* __restrict__ weight,
+                                           const float* __restrict__ scale, float mult, int hidden, int groups, float eps,
+                                           float* out_x, float* copy_in, const float* history, int64_t history_stride,
+                                           const float* __restrict__ mix, int mix_count, float* mixed_x, T* cast) {
+  extern __shared__ float squares[];  // [hidden / 4]
+  __shared__ float rstd[kMaxGroups];
+  wait_for_predecessor();
+  let_successor_start();
+  const int64_t row = static_cast<int64_t>(blockIdx.x) * hidden;
+  const int fours = hidden / 4, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+  float4 d[kFoursPerThread];
+#pragma unroll
+  for (int j = 0; j < kFoursPerThread; ++j) {
+    const int f = threadIdx.x + j * blockDim.x;
+    if (f < fours) {
+      d[j] = Four<T>::load(delta + row + 4 * f);
+      squares[f] = d[j].x * d[j].x + d[j].y * d[j].y + d[j].z * d[j].z + d[j].w * d[j].w;
+    }
+  }
+  __syncthreads();
+  const int per_group = fours / groups;
+  for (int g = warp; g < groups; g += warps) {
+    float ss = 0.f;
+    for (int f = lane; f < per_group; f += 32) ss += squares[g * per_group + f];
+    ss = warp_sum(ss);
+    if (lane == 0) rstd[g] = 1.f / sqrtf(ss / static_cast<float>(4 * per_group) + eps);
+  }
+  __syncthreads();
+#pragma unroll
+  for (int j = 0; j < kFoursPerThread; ++j) {
+    const int f = threadIdx.x + j * blockDim.x;
+    if (f >= fours) continue;
+    const int i = 4 * f;
+    const float r = rstd[f / per_group];
+    const float4 before = *reinterpret_cast<const float4*>(in_x + row + i);
+    const float4 w = *reinterpret_cast<const float4*>(weight + i);
+    const float4 sc = scale ? *reinterpret_cast<const float4*>(scale + i) : make_float4(1.f, 1.f, 1.f, 1.f);
+    float4 v;
+    v.x = before.x + mult * sc.x * (d[j].x * r * w.x);
+    v.y = before.y + mult * sc.y * (d[j].y * r * w.y);
+    v.z = before.z + mult * sc.z * (d[j].z * r * w.z);
+    v.w = before.w + mult * sc.w * (d[j].w * r * w.w);
+    if (copy_in) *reinterpret_cast<float4*>(copy_in + row + i) = before;
+    *reinterpret_cast<float4*>(out_x + row + i) = v;
+    float4 next = v;
+    if (mix) {
+      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+      for (int k = 0; k + 1 < mix_count; ++k) {
+        const float m = mix[k];
+        const float4 h = *reinterpret_cast<const float4*>(history + k * history_stride + row + i);
+        acc.x = fmaf(m, h.x, acc.x), acc.y = fmaf(m, h.y, acc.y), acc.z = fmaf(m, h.z, acc.z), acc.w = fmaf(m, h.w, acc.w);
+      }
+      const float m = mix[mix_count - 1];
+      next = make_float4(fmaf(m, v.x, acc.x), fmaf(m, v.y, acc.y), fmaf(m, v.z, acc.z), fmaf(m, v.w, acc.w));
+      *reinterpret_cast<float4*>(mixed_x + row + i) = next;
+    }
+    if (cast) Four<T>::store(cast + row + i, next);
+  }
+}
+
+// PolyNorm with 16-byte (float) or 8-byte (bfloat16) accesses. The row is read twice (the second
+// time from L1 / L2): kept in registers it cost 72 registers a thread and left one block per SM.
+template <typename T>
+__global__ void poly_norm_vec_kernel(const T* z, const float* __restrict__ coefficients, int width, float eps, T* out) {
+  __shared__ float scratch[32];
+  const float a = coefficients[0], b = coefficients[1], c = coefficients[2], e = coefficients[3];
+  wait_for_predecessor();
+  let_successor_start();
+  const T* zr = z + static_cast<int64_t>(blockIdx.x) * width;
+  const int fours = width / 4;
+  float s1 = 0.f, s2 = 0.f, s3 = 0.f;
+  for (int f = threadIdx.x; f < fours; f += blockDim.x) {
+    const float4 v = Four<T>::load(zr + 4 * f);
+    const float x2 = v.x * v.x, y2 = v.y * v.y, z2 = v.z * v.z, w2 = v.w * v.w;
+    s1 += x2 + y2 + z2 + w2;
+    s2 += x2 * x2 + y2 * y2 + z2 * z2 + w2 * w2;
+    s3 += x2 * x2 * x2 + y2 * y2 * y2 + z2 * z2 * z2 + w2 * w2 * w2;
+  }
+  const float n = static_cast<float>(width);
+  const float r1 = 1.f / sqrtf(block_sum(s1, scratch) / n + eps);
+  const float r2 = 1.f / sqrtf(block_sum(s2, scratch) / n + eps);
+  const float r3 = 1.f / sqrtf(block_sum(s3, scratch) / n + eps);
+  T* o = out + static_cast<int64_t>(blockIdx.x) * width;
+  const auto act = [&](float x) { return a * (x * r1) + b * (x * x * r2) + c * (x * x * x * r3) + e; };
+  for (int f = threadIdx.x; f < fours; f += blockDim.x) {
+    const float4 v = Four<T>::load(zr + 4 * f);
+    Four<T>::store(o + 4 * f, make_float4(act(v.x), act(v.y), act(v.z), act(v.w)));
+  }
+}
+
+bool aligned16(const void* p) { return reinterpret_cast<uintptr_t>(p) % 16 == 0; }
+
 int row_threads(int hidden) { return hidden >= 4096 ? 512 : (hidden >= 1024 ? 256 : 128); }
 
 }  // namespace
@@ -139,6 +263,21 @@ B200_API int b200_branch_norm_add(const float* in_x, const void* delta, const fl
                "branch_norm_add: %d columns do not cut into %d groups", hidden, groups);
   B200_REQUIRE(!mix || (mix_count >= 1 && mixed_x && (mix_count == 1 || history)), "branch_norm_add: bad depth mix");
   const int threads = row_threads(hidden);
+  const bool vec = (hidden / groups) % 4 == 0 && hidden <= 4 * kFoursPerThread * threads && aligned16(in_x) && aligned16(delta) &&
+                   aligned16(weight) && aligned16(scale) && aligned16(out_x) && aligned16(copy_in) && aligned16(history) &&
+                   aligned16(mixed_x) && aligned16(cast) && history_stride % 4 == 0;
+  if (vec && (dtype == DTYPE_F32 || dtype == DTYPE_BF16)) {
+    const size_t smem = sizeof(float) * (hidden / 4);
+    if (dtype == DTYPE_F32)
+      launch_kernel(branch_norm_add_vec_kernel<float>, dim3(rows), dim3(threads), smem, stream, in_x,
+                    static_cast<const float*>(delta), weight, scale, mult, hidden, groups, eps, out_x, copy_in, history,
+                    history_stride, mix, mix_count, mixed_x, static_cast<float*>(cast));
+    else
+      launch_kernel(branch_norm_add_vec_kernel<__nv_bfloat16>, dim3(rows), dim3(threads), smem, stream, in_x,
+                    static_cast<const __nv_bfloat16*>(delta), weight, scale, mult, hidden, groups, eps, out_x, copy_in, history,
+                    history_stride, mix, mix_count, mixed_x, static_cast<__nv_bfloat16*>(cast));
+    return b200_check_launch("branch_norm_add");
+  }
   if (dtype == DTYPE_F32) {
     launch_kernel(branch_norm_add_kernel<float>, dim3(rows), dim3(threads), 0, stream, in_x, static_cast<const float*>(delta),
                   weight, scale, mult, hidden, groups, eps, out_x, copy_in, history, history_stride, mix, mix_count, mixed_x,
@@ -194,6 +333,16 @@ B200_API int b200_poly_norm(const void* z, const float* coefficients, int rows, 
   if (rows == 0) return 0;
   B200_REQUIRE(rows > 0 && width > 0, "poly_norm: bad sizes");
   const int threads = row_threads(width);
+  if (width % 4 == 0 && aligned16(z) && aligned16(out) &&
+      (dtype == DTYPE_F32 || (dtype == DTYPE_BF16 && width % 8 == 0))) {
+    if (dtype == DTYPE_F32)
+      launch_kernel(poly_norm_vec_kernel<float>, dim3(rows), dim3(threads), 0, stream, static_cast<const float*>(z), coefficients,
+                    width, eps, static_cast<float*>(out));
+    else
+      launch_kernel(poly_norm_vec_kernel<__nv_bfloat16>, dim3(rows), dim3(threads), 0, stream,
+                    static_cast<const __nv_bfloat16*>(z), coefficients, width, eps, static_cast<__nv_bfloat16*>(out));
+    return b200_check_launch("poly_norm");
+  }
   if (dtype == DTYPE_F32) {
     launch_kernel(poly_norm_kernel<float>, dim3(rows), dim3(threads), 0, stream, static_cast<const float*>(z), coefficients,
                   width, eps, static_cast<float*>(out));

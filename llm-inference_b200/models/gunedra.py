@@ -60,6 +60,7 @@ def gunedra_recipe(config: GunedraConfig) -> ModelRecipe:
                     feed_forward_norm=norm(prefix + "norm2") if mlp is not None else None, hidden_size=hidden,
                     mult=config.residual_mult, mixer_scale=prefix + "ls1", feed_forward_scale=prefix + "ls2",
                     depth_mix=dict(tensor=prefix + "dwa", index=index, layers=len(config.layers)),
+                    unused=() if mlp is not None else (prefix + "norm2", prefix + "ls2"),
                 ),
             )
         )

@@ -87,7 +87,7 @@ class PostNormResidualBlock(Part):
 
     def __init__(self, *, mixer: PartSpec, feed_forward: PartSpec | None, mixer_norm: PartSpec, feed_forward_norm: PartSpec | None,
                  hidden_size: int, mult: float = 1.0, mixer_scale: str | None = None, feed_forward_scale: str | None = None,
-                 depth_mix: dict | None = None) -> None:
+                 depth_mix: dict | None = None, unused: tuple[str, ...] = ()) -> None:
         self.hidden_size, self.mult = hidden_size, float(mult)
         self.mixer_norm = build_part("norm", mixer_norm)
         self.mixer = build_part("mixer", mixer)
@@ -96,6 +96,9 @@ class PostNormResidualBlock(Part):
         self.parts = tuple(p for p in (self.mixer_norm, self.mixer, self.feed_forward_norm, self.feed_forward) if p is not None)
         self.graph_safe = all(p.graph_safe for p in self.parts)
         self.scale_names = (mixer_scale, feed_forward_scale if feed_forward is not None else None)
+        # A checkpoint may carry the second branch's scale although the layer has no feed-forward; it is read past.
+        # (``unused`` names further per-column tensors of that kind.)
+        self.unused_names = ([feed_forward_scale] if feed_forward is None and feed_forward_scale else []) + [n for n in unused if n != feed_forward_scale]
         self.scales: list[torch.Tensor | None] = [None, None]
         self.depth_mix = dict(depth_mix) if depth_mix else None
         self.mix: torch.Tensor | None = None
@@ -105,6 +108,7 @@ class PostNormResidualBlock(Part):
 
         specs = [spec for part in self.parts for spec in part.tensor_specs()]
         specs += [TensorSpec(name, (self.hidden_size,), init="one_plus_normal") for name in self.scale_names if name]
+        specs += [TensorSpec(name, (self.hidden_size,), init="one_plus_normal", optional=True) for name in self.unused_names]
         if self.depth_mix:
             specs.append(TensorSpec(self.depth_mix["tensor"], (self.depth_mix["index"] + 2,), init="half_plus_normal"))
         return specs

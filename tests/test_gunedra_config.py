@@ -65,6 +65,9 @@ def test_the_recipe_asks_for_exactly_the_tensors_of_the_design(tmp_path):
     folder = write_folder(tmp_path / "m", bare, draw_weights(ALPHA, 1))
     loaded = load_weights(folder, entry.recipe(parsed).tensor_specs())
     assert loaded["l1.mix.a1"].shape == (5, 48) and loaded["l3.mix.g2"].shape == (16, 2)
+    # a layer without a feed-forward may still carry its second norm and scale: they are read past
+    extra = dict(draw_weights(ALPHA, 1), **{"l2.norm2": torch.ones(48, dtype=torch.bfloat16), "l2.ls2": torch.ones(48, dtype=torch.bfloat16)})
+    load_weights(write_folder(tmp_path / "x", bare, extra), entry.recipe(parsed).tensor_specs())
     # ... and every other mismatch is still named
     broken = draw_weights(ALPHA, 1)
     broken["l0.mix.sink"] = broken["l0.mix.sink"][:2]

@@ -13,7 +13,7 @@
 
 namespace {
 
-constexpr int kMaxGroups = 64;
+constexpr int kMaxGroups = 1024;
 
 // 1 / sqrt(mean(d^2) + eps) of every group of row `d`, by the block's warps (one group per warp
 // and turn, lanes stride through it, a fixed tree adds the lanes), into rstd[groups].

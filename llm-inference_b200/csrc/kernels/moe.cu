@@ -1,0 +1,383 @@
+// A routed feed-forward: the router's choice, the tokens grouped by expert, the experts' two
+// products over those groups, and the weighted sum; plus the clamped gated activation of a dense
+// expert of the same form.
+//
+// Router (one warp per token, all 32-bit): s = sigmoid(z); the experts form `groups` equal groups of
+// neighbours, a group scores the sum of its two largest s, only experts of the `keep` best groups can
+// be chosen; the `top` largest s among them are chosen (ties: the lower index), and their weights are
+// s / (sum of the chosen s + 1e-20) * scale.
+//
+// Expert: g = min(W_gate h, limit), u = clamp(W_up h, -limit, limit), y = g sigmoid(1.702 g) (u + 1),
+// output W_down y.
+//
+// Grouping: every (token, choice) pair is a slot. `moe_sort` (one block) counts the slots of each
+// expert, gives each expert a run of whole tiles of kTileM sorted places and writes, per place, the
+// slot it holds (-1: padding) and, per tile, its expert. The two product kernels walk tiles: a tile's
+// rows share one expert's weights. Each output number is one thread's sum over K in a fixed order, so
+// a slot's result does not depend on which other slots share its tile, and the final sum over a
+// token's choices runs in the router's order: nothing depends on the batch.
+#include "common.cuh"
+
+namespace {
+
+constexpr int kTileM = 32;
+constexpr int kTileN = 32;
+constexpr int kTileK = 32;
+constexpr int kGemmThreads = 256;  // 8 row groups of 4 rows x 32 columns
+
+__device__ __forceinline__ float sigmoid_f(float x) { return 1.f / (1.f + expf(-x)); }
+
+__device__ __forceinline__ float clamped_glu(float g, float u, float limit) {
+  g = fminf(g, limit);
+  u = fminf(fmaxf(u, -limit), limit);
+  return g * sigmoid_f(1.702f * g) * (u + 1.f);
+}
+
+// The lane holding the largest value (ties: the lowest index) among the lanes' candidates.
+__device__ __forceinline__ void warp_argmax(float& value, int& index) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float other = __shfl_xor_sync(0xffffffffu, value, o);
+    const int other_index = __shfl_xor_sync(0xffffffffu, index, o);
+    if (other > value || (other == value && other_index < index)) {
+      value = other;
+      index = other_index;
+    }
+  }
+}
+
+// z [tokens][experts] -> ids [tokens][top], weights [tokens][top]. Shared memory per warp:
+// experts scores + groups group scores.
+__global__ void moe_route_kernel(const float* z, int tokens, int experts, int groups, int keep, int top, float scale, int* ids,
+                                 float* weights) {
+  extern __shared__ float route_smem[];
+  wait_for_predecessor();
+  let_successor_start();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+  const int t = blockIdx.x * warps + warp;
+  if (t >= tokens) return;
+  float* s = route_smem + warp * (experts + groups);
+  float* gs = s + experts;
+  const int size = experts / groups;
+  for (int e = lane; e < experts; e += 32) s[e] = sigmoid_f(z[static_cast<int64_t>(t) * experts + e]);
+  __syncwarp();
+  for (int g = lane; g < groups; g += 32) {
+    float first = -INFINITY, second = -INFINITY;
+    for (int i = 0; i < size; ++i) {
+      const float v = s[g * size + i];
+      if (v > first) {
+        second = first;
+        first = v;
+      } else if (v > second) {
+        second = v;
+      }
+    }
+    gs[g] = size > 1 ? first + second : first;
+  }
+  __syncwarp();
+  // Keep the best groups: the others' experts leave the contest.
+  if (keep < groups) {
+    for (int round = 0; round < keep; ++round) {
+      float best = -INFINITY;
+      int at = 0x7fffffff;
+      for (int g = lane; g < groups; g += 32)
+        if (gs[g] > best) best = gs[g], at = g;  // indices grow along a lane: the first maximum stays
+      warp_argmax(best, at);
+      if (lane == 0) gs[at] = -INFINITY;  // marks a kept group
+      __syncwarp();
+    }
+    for (int e = lane; e < experts; e += 32)
+      if (gs[e / size] != -INFINITY) s[e] = -INFINITY;
+    __syncwarp();
+  }
+  float sum = 0.f, mine = 0.f;
+  int mine_id = 0;
+  for (int j = 0; j < top; ++j) {
+    float best = -INFINITY;
+    int at = 0x7fffffff;
+    for (int e = lane; e < experts; e += 32)
+      if (s[e] > best) best = s[e], at = e;
+    warp_argmax(best, at);
+    if (at >= experts) at = 0, best = 0.f;  // cannot happen with a valid configuration and finite logits
+    sum += best;
+    if (lane == j % 32 && j < 32) mine = best, mine_id = at;
+    if (j >= 32 && lane == 0) {  // more than 32 choices: written unnormalised, fixed up below
+      ids[static_cast<int64_t>(t) * top + j] = at;
+      weights[static_cast<int64_t>(t) * top + j] = best;
+    }
+    if (lane == 0) s[at] = -INFINITY;
+    __syncwarp();
+  }
+  const float factor = scale / (sum + 1e-20f);
+  if (lane < top) {
+    ids[static_cast<int64_t>(t) * top + lane] = mine_id;
+    weights[static_cast<int64_t>(t) * top + lane] = mine * factor;
+  }
+  if (lane == 0)
+    for (int j = 32; j < top; ++j) weights[static_cast<int64_t>(t) * top + j] *= factor;
+}
+
+// One block. ids [slots]; place_slot [capacity]; tile_expert [max_tiles]; num_tiles [1].
+__global__ void moe_sort_kernel(const int* ids, int slots, int experts, int capacity, int* place_slot, int* tile_expert, int* num_tiles) {
+  extern __shared__ int sort_smem[];  // counts [experts], cursor [experts]
+  int* counts = sort_smem;
+  int* cursor = counts + experts;
+  wait_for_predecessor();
+  let_successor_start();
+  for (int e = threadIdx.x; e < experts; e += blockDim.x) counts[e] = 0;
+  for (int i = threadIdx.x; i < capacity; i += blockDim.x) place_slot[i] = -1;
+  __syncthreads();
+  for (int i = threadIdx.x; i < slots; i += blockDim.x) {
+    const int e = ids[i];
+    if (e >= 0 && e < experts) atomicAdd(&counts[e], 1);
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int tile = 0;
+    for (int e = 0; e < experts; ++e) {
+      cursor[e] = tile * kTileM;
+      const int tiles = (counts[e] + kTileM - 1) / kTileM;
+      for (int i = 0; i < tiles; ++i) tile_expert[tile + i] = e;
+      tile += tiles;
+    }
+    *num_tiles = tile;
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < slots; i += blockDim.x) {
+    const int e = ids[i];
+    if (e >= 0 && e < experts) place_slot[atomicAdd(&cursor[e], 1)] = i;
+  }
+}
+
+// act[place][n] = glu(h[token(place)] . W_gate[e][n], h . W_up[e][n]) for the tile's expert e.
+// w_gate_up [experts][2 * ff][width]: rows 0 .. ff are the gate's, the rest the up projection's.
+template <typename T>
+__global__ void __launch_bounds__(kGemmThreads)
+moe_gate_up_kernel(const T* h, const T* __restrict__ weight, const int* place_slot, const int* tile_expert, const int* num_tiles, int top,
+                   int width, int ff, float limit, T* act) {
+  __shared__ float a_tile[kTileM][kTileK + 1];
+  __shared__ float g_tile[kTileN][kTileK + 1];
+  __shared__ float u_tile[kTileN][kTileK + 1];
+  __shared__ int row_token[kTileM];
+  wait_for_predecessor();
+  let_successor_start();
+  const int tile = blockIdx.x;
+  if (tile >= *num_tiles) return;
+  const int expert = tile_expert[tile];
+  const int n0 = blockIdx.y * kTileN;
+  const int tid = threadIdx.x, tx = tid & 31, ty = tid >> 5;
+  if (tid < kTileM) {
+    const int slot = place_slot[tile * kTileM + tid];
+    row_token[tid] = slot < 0 ? -1 : slot / top;
+  }
+  __syncthreads();
+  const T* wg = weight + static_cast<int64_t>(expert) * 2 * ff * width;
+  const T* wu = wg + static_cast<int64_t>(ff) * width;
+  float acc_g[4] = {0.f, 0.f, 0.f, 0.f}, acc_u[4] = {0.f, 0.f, 0.f, 0.f};
+  for (int k0 = 0; k0 < width; k0 += kTileK) {
+    for (int idx = tid; idx < kTileM * kTileK; idx += kGemmThreads) {
+      const int r = idx / kTileK, c = idx % kTileK;
+      const int token = row_token[r];
+      a_tile[r][c] = (token >= 0 && k0 + c < width) ? to_f32<T>(h[static_cast<int64_t>(token) * width + k0 + c]) : 0.f;
+      const int n = n0 + r;
+      const bool in = n < ff && k0 + c < width;
+      g_tile[r][c] = in ? to_f32<T>(wg[static_cast<int64_t>(n) * width + k0 + c]) : 0.f;
+      u_tile[r][c] = in ? to_f32<T>(wu[static_cast<int64_t>(n) * width + k0 + c]) : 0.f;
+    }
+    __syncthreads();
+#pragma unroll 8
+    for (int kk = 0; kk < kTileK; ++kk) {
+      const float bg = g_tile[tx][kk], bu = u_tile[tx][kk];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float a = a_tile[ty * 4 + i][kk];
+        acc_g[i] = fmaf(a, bg, acc_g[i]);
+        acc_u[i] = fmaf(a, bu, acc_u[i]);
+      }
+    }
+    __syncthreads();
+  }
+  const int n = n0 + tx;
+  if (n >= ff) return;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int r = ty * 4 + i;
+    if (row_token[r] >= 0)
+      act[(static_cast<int64_t>(tile) * kTileM + r) * ff + n] = from_f32<T>(clamped_glu(acc_g[i], acc_u[i], limit));
+  }
+}
+
+// out[slot(place)][n] = act[place] . W_down[e][n] (32-bit, not yet weighted). w_down [experts][width][ff].
+template <typename T>
+__global__ void __launch_bounds__(kGemmThreads)
+moe_down_kernel(const T* act, const T* __restrict__ weight, const int* place_slot, const int* tile_expert, const int* num_tiles,
+                int width, int ff, float* out) {
+  __shared__ float a_tile[kTileM][kTileK + 1];
+  __shared__ float b_tile[kTileN][kTileK + 1];
+  __shared__ int row_slot[kTileM];
+  wait_for_predecessor();
+  let_successor_start();
+  const int tile = blockIdx.x;
+  if (tile >= *num_tiles) return;
+  const int expert = tile_expert[tile];
+  const int n0 = blockIdx.y * kTileN;
+  const int tid = threadIdx.x, tx = tid & 31, ty = tid >> 5;
+  if (tid < kTileM) row_slot[tid] = place_slot[tile * kTileM + tid];
+  __syncthreads();
+  const T* w = weight + static_cast<int64_t>(expert) * width * ff;
+  float acc[4] = {0.f, 0.f, 0.f, 0.f};
+  for (int k0 = 0; k0 < ff; k0 += kTileK) {
+    for (int idx = tid; idx < kTileM * kTileK; idx += kGemmThreads) {
+      const int r = idx / kTileK, c = idx % kTileK;
+      a_tile[r][c] = (row_slot[r] >= 0 && k0 + c < ff) ? to_f32<T>(act[(static_cast<int64_t>(tile) * kTileM + r) * ff + k0 + c]) : 0.f;
+      const int n = n0 + r;
+      b_tile[r][c] = (n < width && k0 + c < ff) ? to_f32<T>(w[static_cast<int64_t>(n) * ff + k0 + c]) : 0.f;
+    }
+    __syncthreads();
+#pragma unroll 8
+    for (int kk = 0; kk < kTileK; ++kk) {
+      const float b = b_tile[tx][kk];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) acc[i] = fmaf(a_tile[ty * 4 + i][kk], b, acc[i]);
+    }
+    __syncthreads();
+  }
+  const int n = n0 + tx;
+  if (n >= width) return;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int slot = row_slot[ty * 4 + i];
+    if (slot >= 0) out[static_cast<int64_t>(slot) * width + n] = acc[i];
+  }
+}
+
+// out[t] = sum_j weights[t][j] * expert_out[t * top + j] (+ shared[t]), in the order of j.
+template <typename T>
+__global__ void moe_combine_kernel(const float* expert_out, const float* weights, const T* shared, int top, int width, T* out) {
+  wait_for_predecessor();
+  let_successor_start();
+  const int t = blockIdx.x;
+  for (int d = threadIdx.x; d < width; d += blockDim.x) {
+    float acc = 0.f;
+    for (int j = 0; j < top; ++j)
+      acc = fmaf(weights[static_cast<int64_t>(t) * top + j], expert_out[(static_cast<int64_t>(t) * top + j) * width + d], acc);
+    if (shared) acc += to_f32<T>(shared[static_cast<int64_t>(t) * width + d]);
+    out[static_cast<int64_t>(t) * width + d] = from_f32<T>(acc);
+  }
+}
+
+// gate_up rows are [gate (ff) | up (ff)].
+template <typename T>
+__global__ void clamped_glu_kernel(const T* gate_up, int64_t rows, int ff, float limit, T* out) {
+  wait_for_predecessor();
+  let_successor_start();
+  const int64_t total = rows * ff;
+  for (int64_t idx = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; idx < total; idx += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int64_t r = idx / ff;
+    const int c = static_cast<int>(idx % ff);
+    out[idx] = from_f32<T>(clamped_glu(to_f32<T>(gate_up[r * 2 * ff + c]), to_f32<T>(gate_up[r * 2 * ff + ff + c]), limit));
+  }
+}
+
+}  // namespace
+
+B200_API int b200_moe_tile_rows() { return kTileM; }
+
+B200_API int b200_moe_route(const float* z, int tokens, int experts, int groups, int keep, int top, float scale, int* ids, float* weights,
+                            cudaStream_t stream) {
+  if (tokens == 0) return 0;
+  B200_REQUIRE(tokens > 0 && experts > 0 && groups > 0 && experts % groups == 0 && keep > 0 && keep <= groups && top > 0 &&
+                   top <= keep * (experts / groups),
+               "moe_route: %d experts in %d groups, %d kept, %d chosen", experts, groups, keep, top);
+  const int warps = 4;
+  const size_t smem = sizeof(float) * warps * (experts + groups);
+  B200_REQUIRE(smem <= 48 * 1024, "moe_route: %d experts do not fit shared memory", experts);
+  launch_kernel(moe_route_kernel, dim3((tokens + warps - 1) / warps), dim3(32 * warps), smem, stream, z, tokens, experts, groups, keep,
+                top, scale, ids, weights);
+  return b200_check_launch("moe_route");
+}
+
+B200_API int b200_moe_sort(const int* ids, int slots, int experts, int capacity, int* place_slot, int* tile_expert, int* num_tiles,
+                           cudaStream_t stream) {
+  if (slots == 0) return 0;
+  B200_REQUIRE(slots > 0 && experts > 0 && capacity >= slots, "moe_sort: bad sizes");
+  B200_REQUIRE(capacity % kTileM == 0 && capacity / kTileM >= (slots + experts * (kTileM - 1)) / kTileM,
+               "moe_sort: %d places do not hold %d slots of %d experts in whole tiles", capacity, slots, experts);
+  const size_t smem = sizeof(int) * 2 * experts;
+  B200_REQUIRE(smem <= 48 * 1024, "moe_sort: too many experts");
+  launch_kernel(moe_sort_kernel, dim3(1), dim3(1024), smem, stream, ids, slots, experts, capacity, place_slot, tile_expert, num_tiles);
+  return b200_check_launch("moe_sort");
+}
+
+B200_API int b200_moe_gate_up(const void* h, const void* weight, const int* place_slot, const int* tile_expert, const int* num_tiles,
+                              int max_tiles, int top, int width, int ff, float limit, void* act, int dtype, cudaStream_t stream) {
+  if (max_tiles == 0) return 0;
+  B200_REQUIRE(max_tiles > 0 && top > 0 && width > 0 && ff > 0 && limit > 0.f, "moe_gate_up: bad sizes");
+  const dim3 grid(max_tiles, (ff + kTileN - 1) / kTileN);
+  B200_REQUIRE(grid.y <= 65535, "moe_gate_up: too many columns");
+  if (dtype == DTYPE_F32) {
+    launch_kernel(moe_gate_up_kernel<float>, grid, dim3(kGemmThreads), 0, stream, static_cast<const float*>(h),
+                  static_cast<const float*>(weight), place_slot, tile_expert, num_tiles, top, width, ff, limit, static_cast<float*>(act));
+  } else if (dtype == DTYPE_BF16) {
+    launch_kernel(moe_gate_up_kernel<__nv_bfloat16>, grid, dim3(kGemmThreads), 0, stream, static_cast<const __nv_bfloat16*>(h),
+                  static_cast<const __nv_bfloat16*>(weight), place_slot, tile_expert, num_tiles, top, width, ff, limit,
+                  static_cast<__nv_bfloat16*>(act));
+  } else {
+    return b200_fail("moe_gate_up: unknown dtype %d", dtype);
+  }
+  return b200_check_launch("moe_gate_up");
+}
+
+B200_API int b200_moe_down(const void* act, const void* weight, const int* place_slot, const int* tile_expert, const int* num_tiles,
+                           int max_tiles, int width, int ff, float* out, int dtype, cudaStream_t stream) {
+  if (max_tiles == 0) return 0;
+  B200_REQUIRE(max_tiles > 0 && width > 0 && ff > 0, "moe_down: bad sizes");
+  const dim3 grid(max_tiles, (width + kTileN - 1) / kTileN);
+  B200_REQUIRE(grid.y <= 65535, "moe_down: too many columns");
+  if (dtype == DTYPE_F32) {
+    launch_kernel(moe_down_kernel<float>, grid, dim3(kGemmThreads), 0, stream, static_cast<const float*>(act),
+                  static_cast<const float*>(weight), place_slot, tile_expert, num_tiles, width, ff, out);
+  } else if (dtype == DTYPE_BF16) {
+    launch_kernel(moe_down_kernel<__nv_bfloat16>, grid, dim3(kGemmThreads), 0, stream, static_cast<const __nv_bfloat16*>(act),
+                  static_cast<const __nv_bfloat16*>(weight), place_slot, tile_expert, num_tiles, width, ff, out);
+  } else {
+    return b200_fail("moe_down: unknown dtype %d", dtype);
+  }
+  return b200_check_launch("moe_down");
+}
+
+B200_API int b200_moe_combine(const float* expert_out, const float* weights, const void* shared, int tokens, int top, int width, void* out,
+                              int dtype, cudaStream_t stream) {
+  if (tokens == 0) return 0;
+  B200_REQUIRE(tokens > 0 && top > 0 && width > 0, "moe_combine: bad sizes");
+  const int threads = width >= 1024 ? 256 : 128;
+  if (dtype == DTYPE_F32) {
+    launch_kernel(moe_combine_kernel<float>, dim3(tokens), dim3(threads), 0, stream, expert_out, weights, static_cast<const float*>(shared),
+                  top, width, static_cast<float*>(out));
+  } else if (dtype == DTYPE_BF16) {
+    launch_kernel(moe_combine_kernel<__nv_bfloat16>, dim3(tokens), dim3(threads), 0, stream, expert_out, weights,
+                  static_cast<const __nv_bfloat16*>(shared), top, width, static_cast<__nv_bfloat16*>(out));
+  } else {
+    return b200_fail("moe_combine: unknown dtype %d", dtype);
+  }
+  return b200_check_launch("moe_combine");
+}
+
+B200_API int b200_clamped_glu(const void* gate_up, int rows, int ff, float limit, void* out, int dtype, cudaStream_t stream) {
+  if (rows == 0) return 0;
+  B200_REQUIRE(rows > 0 && ff > 0 && limit > 0.f, "clamped_glu: bad sizes");
+  const int threads = 256;
+  const int64_t total = static_cast<int64_t>(rows) * ff;
+  const int64_t want = (total + threads - 1) / threads;
+  const dim3 grid(static_cast<unsigned>(want < 65535 ? want : 65535));
+  if (dtype == DTYPE_F32) {
+    launch_kernel(clamped_glu_kernel<float>, grid, dim3(threads), 0, stream, static_cast<const float*>(gate_up), static_cast<int64_t>(rows),
+                  ff, limit, static_cast<float*>(out));
+  } else if (dtype == DTYPE_BF16) {
+    launch_kernel(clamped_glu_kernel<__nv_bfloat16>, grid, dim3(threads), 0, stream, static_cast<const __nv_bfloat16*>(gate_up),
+                  static_cast<int64_t>(rows), ff, limit, static_cast<__nv_bfloat16*>(out));
+  } else {
+    return b200_fail("clamped_glu: unknown dtype %d", dtype);
+  }
+  return b200_check_launch("clamped_glu");
+}

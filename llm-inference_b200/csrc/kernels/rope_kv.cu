@@ -15,23 +15,7 @@
 // page that this step does not fill. From then on every row of a page a request holds is either
 // the request's own or zero.
 #include "common.cuh"
-
-// Clears rows `first_row .. page_size` of one (page, kv head) tile, which are contiguous.
-template <typename T>
-__device__ __forceinline__ void clear_page_tail(T* tile, int first_row, int page_size, int head_dim) {
-  if (first_row >= page_size) return;
-  const int64_t begin = static_cast<int64_t>(first_row) * head_dim * sizeof(T);
-  const int64_t end = static_cast<int64_t>(page_size) * head_dim * sizeof(T);
-  unsigned char* base = reinterpret_cast<unsigned char*>(tile);
-  if ((static_cast<int64_t>(head_dim) * sizeof(T)) % 16 == 0 && reinterpret_cast<uintptr_t>(base) % 16 == 0) {
-    for (int64_t at = begin + threadIdx.x * 16; at < end; at += static_cast<int64_t>(blockDim.x) * 16)
-      *reinterpret_cast<uint4*>(base + at) = make_uint4(0u, 0u, 0u, 0u);
-  } else {
-    T* elems = tile + static_cast<int64_t>(first_row) * head_dim;
-    const int count = (page_size - first_row) * head_dim;
-    for (int i = threadIdx.x; i < count; i += blockDim.x) elems[i] = from_f32<T>(0.f);
-  }
-}
+#include "page_tail.cuh"
 
 constexpr int kWideTokens = 64;  // from this many tokens on, one block per token (below)
 

@@ -1,4 +1,4 @@
-from . import attention, block, delta_rule, embedding, feed_forward, latent_attention, norms, positions  # noqa: F401  (register parts)
+from . import attention, block, delta_rule, embedding, feed_forward, gated_attention, hyper, latent_attention, norms, positions, wkv  # noqa: F401  (register parts)
 from .base import (
     KVCacheSpec,
     Part,

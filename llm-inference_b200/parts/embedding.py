@@ -41,13 +41,48 @@ class TokenEmbedding(Part):
         return ops.embedding_scaled(ctx, self.table, self.scale, x, cast)
 
 
+class SinusoidEmbedding(Part):
+    """``x[t] = table[token[t]] * scale + e(p)`` with ``e(p)[2i] = sin(p f_i)``, ``e(p)[2i + 1] = cos(p f_i)``,
+    ``f_i = base^(-2i / hidden)`` and ``p`` the token's position in its request; the sum is 32-bit and fills
+    every one of the token's ``streams`` residual streams (the stream buffer is ``[tokens, streams * hidden]``)."""
+
+    def __init__(self, *, name: str, vocab_size: int, hidden_size: int, scale: float = 1.0, streams: int = 1, base: float = 10000.0) -> None:
+        if hidden_size % 2:
+            raise ValueError("sine and cosine columns alternate: the width must be even")
+        self.name, self.vocab_size, self.hidden_size = name, vocab_size, hidden_size
+        self.scale, self.streams, self.base = float(scale), int(streams), float(base)
+        self.table: torch.Tensor | None = None
+        self.inv_freq: torch.Tensor | None = None
+
+    def tensor_specs(self) -> list[TensorSpec]:
+        return [TensorSpec(self.name, (self.vocab_size, self.hidden_size))]
+
+    def frequencies(self) -> torch.Tensor:
+        """``f_i`` worked out in 64-bit and rounded once to float32."""
+        i = torch.arange(self.hidden_size // 2, dtype=torch.float64)
+        return torch.pow(torch.tensor(self.base, dtype=torch.float64), -2.0 * i / self.hidden_size).to(torch.float32)
+
+    def load(self, tensors, dtype, device) -> None:
+        self.table = tensors[self.name].to(device=device, dtype=dtype).contiguous()
+        self.inv_freq = self.frequencies().to(device)
+
+    def weight_bytes(self) -> int:
+        return 0  # a step reads only its tokens' rows
+
+    def forward(self, ctx: StepContext) -> torch.Tensor:
+        x = ctx.buffer("residual_streams", (ctx.num_tokens, self.streams * self.hidden_size), torch.float32)
+        return ops.embedding_sinusoid(ctx, self.table, self.inv_freq, self.scale, self.streams, x)
+
+
 class OutputHead(Part):
     """``logits = h W^T`` in 32-bit. With ``tied_to`` the matrix is the embedding table and
     the checkpoint need not hold a tensor of its own (python/instinct/export.py:38-41)."""
 
-    def __init__(self, *, name: str, vocab_size: int, hidden_size: int, tied_to: str | None = None, suffix: str = ".weight") -> None:
+    def __init__(self, *, name: str, vocab_size: int, hidden_size: int, tied_to: str | None = None, suffix: str = ".weight",
+                 softcap: float | None = None) -> None:
         self.name, self.vocab_size, self.hidden_size, self.tied_to = name, vocab_size, hidden_size, tied_to
         self.suffix = suffix
+        self.softcap = float(softcap) if softcap else None  # logits <- softcap * tanh(logits / softcap)
         self.weight: torch.Tensor | None = None
 
     def tensor_specs(self) -> list[TensorSpec]:
@@ -69,9 +104,10 @@ class OutputHead(Part):
         return self.weight.numel() * self.weight.element_size()
 
     def forward(self, ctx: StepContext, h: torch.Tensor) -> torch.Tensor:
-        logits = ctx.buffer("logits", (h.shape[0], self.vocab_size), torch.float32, per_token=False)
-        return ops.linear(ctx, h, self.weight, logits)
+        logits = ops.linear(ctx, h, self.weight, ctx.buffer("logits", (h.shape[0], self.vocab_size), torch.float32, per_token=False))
+        return ops.softcap(ctx, logits, self.softcap) if self.softcap else logits
 
 
 register_part("embedding", "token_embedding", TokenEmbedding)
+register_part("embedding", "sinusoid_embedding", SinusoidEmbedding)
 register_part("head", "linear_head", OutputHead)

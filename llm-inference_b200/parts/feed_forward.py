@@ -82,5 +82,78 @@ class PolyNormFeedForward(Part):
         return ops.linear(ctx, act, self.w_down, ctx.buffer("branch", (t, self.hidden_size)))
 
 
+class RoutedExperts(Part):
+    """A mixture of ``experts`` small gated feed-forward layers of which each token uses ``top``, plus an
+    optional shared expert that every token uses.
+
+    Expert (no biases): ``g = min(W_gate h, limit)``, ``u = clamp(W_up h, -limit, limit)``,
+    ``y = g * sigmoid(1.702 g) * (u + 1)``, output ``W_down y``. Router, in 32-bit: ``s = sigmoid(W_router h)``;
+    the experts form ``group_count`` equal groups of neighbours, a group scores the sum of its two
+    largest ``s``, and only experts of the ``group_keep`` best groups can be chosen; the ``top`` largest
+    ``s`` among them are chosen and weighted ``s / (sum of the chosen s + 1e-20) * route_scale``. The output
+    is the weighted sum of the chosen experts' outputs plus the shared expert's.
+
+    The experts' matrices are stacked (``[experts, 2 ff, hidden]`` with the gate rows first, and
+    ``[experts, hidden, ff]``); a step sorts its (token, choice) pairs by expert and the two products
+    walk the sorted runs, so only chosen experts' weights are read. Tensor names: ``prefix + router |
+    e<j>.{gate,up,down} | shared.{gate,up,down}``."""
+
+    def __init__(self, *, prefix: str, hidden_size: int, experts: int, top: int, intermediate_size: int, limit: float,
+                 route_scale: float, group_count: int = 1, group_keep: int = 1, shared_size: int | None = None,
+                 shared_limit: float | None = None) -> None:
+        self.prefix, self.hidden_size = prefix, hidden_size
+        self.experts, self.top, self.intermediate_size, self.limit = int(experts), int(top), int(intermediate_size), float(limit)
+        self.route_scale, self.group_count, self.group_keep = float(route_scale), int(group_count), int(group_keep)
+        self.shared_size = int(shared_size) if shared_size else 0
+        self.shared_limit = float(shared_limit) if shared_limit is not None else self.limit
+        self.w_router = self.w_gate_up = self.w_down = self.w_shared_gate_up = self.w_shared_down = None
+
+    def tensor_specs(self) -> list[TensorSpec]:
+        p, h, i = self.prefix, self.hidden_size, self.intermediate_size
+        specs = [TensorSpec(p + "router", (self.experts, h))]
+        for e in range(self.experts):
+            specs += [TensorSpec(f"{p}e{e}.gate", (i, h)), TensorSpec(f"{p}e{e}.up", (i, h)), TensorSpec(f"{p}e{e}.down", (h, i))]
+        if self.shared_size:
+            s = self.shared_size
+            specs += [TensorSpec(p + "shared.gate", (s, h)), TensorSpec(p + "shared.up", (s, h)), TensorSpec(p + "shared.down", (h, s))]
+        return specs
+
+    def load(self, tensors, dtype, device) -> None:
+        p = self.prefix
+
+        def get(name: str) -> torch.Tensor:
+            return tensors[p + name].to(device=device, dtype=dtype)
+
+        self.w_router = get("router").contiguous()
+        self.w_gate_up = torch.stack([torch.cat([get(f"e{e}.gate"), get(f"e{e}.up")]) for e in range(self.experts)]).contiguous()
+        self.w_down = torch.stack([get(f"e{e}.down") for e in range(self.experts)]).contiguous()
+        if self.shared_size:
+            self.w_shared_gate_up = torch.cat([get("shared.gate"), get("shared.up")]).contiguous()
+            self.w_shared_down = get("shared.down").contiguous()
+
+    def weight_bytes(self) -> int:
+        """What a step reads at most: the router, the shared expert and ``top`` experts per token is the
+        least; counted here is the router, the shared expert and every expert once."""
+        tensors = [self.w_router, self.w_gate_up, self.w_down, self.w_shared_gate_up, self.w_shared_down]
+        return sum(w.numel() * w.element_size() for w in tensors if w is not None)
+
+    def forward(self, ctx: StepContext, h: torch.Tensor) -> torch.Tensor:
+        t, width = ctx.num_tokens, self.hidden_size
+        logits = ops.linear(ctx, h, self.w_router, ctx.buffer("moe_logits", (t, self.experts), torch.float32))
+        ids = ctx.buffer("moe_ids", (t, self.top), torch.int32)
+        weights = ctx.buffer("moe_weights", (t, self.top), torch.float32)
+        ops.moe_route(ctx, logits, self.group_count, self.group_keep, self.top, self.route_scale, ids, weights)
+        expert_out = ops.moe_experts(
+            ctx, h, ids, self.w_gate_up, self.w_down, self.limit, ctx.buffer("moe_expert_out", (t * self.top, width), torch.float32, per_token=False)
+        )
+        shared = None
+        if self.shared_size:
+            gate_up = ops.linear(ctx, h, self.w_shared_gate_up, ctx.buffer("gate_up", (t, 2 * self.shared_size)))
+            act = ops.clamped_glu(ctx, gate_up, self.shared_limit, ctx.buffer("act", (t, self.shared_size)))
+            shared = ops.linear(ctx, act, self.w_shared_down, ctx.buffer("moe_shared", (t, width)))
+        return ops.moe_combine(ctx, expert_out, weights, shared, ctx.buffer("branch", (t, width)))
+
+
 register_part("feed_forward", "swiglu", SwiGLU)
 register_part("feed_forward", "poly_norm", PolyNormFeedForward)
+register_part("feed_forward", "routed_experts", RoutedExperts)

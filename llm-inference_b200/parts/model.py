@@ -9,6 +9,7 @@ from typing import Any
 import torch
 
 from ..weights.loader import TensorSpec
+from . import ops
 from .base import KVCacheSpec, PartSpec, StateSpec, build_part
 from .context import CacheView, StepContext
 
@@ -163,7 +164,7 @@ class Model:
         if ctx.logit_rows.numel() == 0:
             return torch.empty((0, self.head.vocab_size), dtype=torch.float32, device=ctx.device)
         with mark("head"):
-            if not isinstance(delta, torch.Tensor) and delta is not None and not getattr(self.final_norm, "foldable", False):
+            if isinstance(delta, ops.FoldedRows) and not getattr(self.final_norm, "foldable", False):
                 delta = None  # the stream is current; this norm knows nothing of the folded form
             h = self.final_norm.forward(ctx, x, delta, rows=ctx.logit_rows, out_name="normed_rows")
             return self.head.forward(ctx, h)

@@ -790,3 +790,248 @@ def delta_output(
         c_float(eps), ptr(out), c_int(dtype_code(out.dtype)), ctx.stream,
     )
     return out
+
+
+# -- several residual streams per token, sinusoidal embedding, soft cap -----------------------------------
+
+
+@dataclass
+class PendingBranch:
+    """A sublayer's output that is not in the residual streams yet, with the weights that put it
+    there: ``x_t <- sum_s mix[s, t] x_s + out[t] * y`` (``mix`` None: the identity). The norm kernel
+    that reads the streams next does the write on its way."""
+
+    y: torch.Tensor
+    mix: torch.Tensor | None
+    out: torch.Tensor | None
+
+
+def embedding_sinusoid(ctx: StepContext, table: torch.Tensor, inv_freq: torch.Tensor, scale: float, streams: int, out: torch.Tensor) -> torch.Tensor:
+    """``out[t, s] = table[token[t]] * scale + e(position[t])`` for every stream ``s``; ``e`` alternates the
+    sine and cosine of ``position * inv_freq[i]``. ``out`` is ``[tokens, streams * hidden]`` float32."""
+    vocab, hidden = table.shape
+    _need(tuple(out.shape) == (ctx.num_tokens, streams * hidden) and out.dtype == torch.float32 and out.is_contiguous(), "embedding: bad output")
+    _need(inv_freq.dtype == torch.float32 and inv_freq.numel() == hidden // 2 and hidden % 2 == 0, "embedding: one frequency per column pair")
+    ctx.lib.call(
+        "b200_embedding_sinusoid", ptr(table), ptr(ctx.token_ids), ptr(ctx.positions), ptr(inv_freq), c_float(scale), ptr(out),
+        c_int(ctx.num_tokens), c_int(streams), c_int(hidden), c_int(vocab), c_int(dtype_code(table.dtype)), ptr(ctx.err), ctx.stream,
+    )
+    return out
+
+
+def hyper_norm(
+    ctx: StepContext, x: torch.Tensor, pending: PendingBranch | None, in_w: torch.Tensor | None, weight: torch.Tensor, streams: int,
+    eps: float, out: torch.Tensor, rows: torch.Tensor | None = None,
+) -> torch.Tensor:
+    """Writes ``pending`` into the streams ``x`` (``[tokens, streams * hidden]``; stored back unless ``rows``
+    gathers), then ``out = rms_norm(sum_s in_w[s] x_s) * weight`` (``in_w`` None: the plain sum)."""
+    hidden = weight.numel()
+    count = x.shape[0] if rows is None else rows.shape[0]
+    _need(x.dtype == torch.float32 and x.is_contiguous() and x.shape[1] == streams * hidden, "hyper_norm: the streams are contiguous float32")
+    _need(weight.dtype == torch.float32 and tuple(out.shape) == (count, hidden) and out.is_contiguous(), "hyper_norm: bad weight or output")
+    y = mix = out_w = None
+    if pending is not None:
+        y, mix, out_w = pending.y, pending.mix, pending.out
+        _need(tuple(y.shape) == (x.shape[0], hidden) and y.is_contiguous() and y.dtype == out.dtype, "hyper_norm: bad branch output")
+        _need(mix is not None and mix.dtype == torch.float32 and mix.numel() == streams * streams and out_w.dtype == torch.float32 and out_w.numel() == streams, "hyper_norm: bad mixing weights")
+    _need(in_w is None or (in_w.dtype == torch.float32 and in_w.numel() == streams), "hyper_norm: bad read weights")
+    ctx.lib.call(
+        "b200_hyper_norm", ptr(x), ptr(y), ptr(mix), ptr(out_w), ptr(in_w), ptr(weight), ptr(rows), c_int(count), c_int(streams),
+        c_int(hidden), c_float(eps), ptr(out), c_int(dtype_code(out.dtype)), ctx.stream,
+    )
+    return out
+
+
+def softcap(ctx: StepContext, logits: torch.Tensor, cap: float) -> torch.Tensor:
+    """``logits <- cap * tanh(logits / cap)`` in place (float32)."""
+    _need(logits.dtype == torch.float32 and logits.is_contiguous(), "softcap: logits are contiguous float32")
+    ctx.lib.call("b200_softcap", ptr(logits), c_int64(logits.numel()), c_float(cap), ctx.stream)
+    return logits
+
+
+# -- the recurrent mixer with a decay per channel and a bonus for the current token ----------------------
+
+
+def wkv_shift_mix(ctx: StepContext, h: torch.Tensor, shift: torch.Tensor, mu: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """``out[s, t] = h[t] + (h[t - 1] - h[t]) * mu[s]`` (a request's first token of the step takes its slot of
+    ``shift`` for ``h[t - 1]``); the slot then moves on to the request's last input of the step."""
+    tokens, hidden = h.shape
+    blends = mu.shape[0]
+    _need(h.is_contiguous() and tuple(out.shape) == (blends, tokens, hidden) and out.is_contiguous() and out.dtype == h.dtype, "wkv_shift_mix: bad operands")
+    _need(mu.dtype == torch.float32 and mu.is_contiguous() and mu.shape[1] == hidden, "wkv_shift_mix: blends are float32 [n, hidden]")
+    _need(shift.dtype == h.dtype and tuple(shift.shape[1:]) == (hidden,) and shift.is_contiguous(), "wkv_shift_mix: bad slot array")
+    ctx.lib.call(
+        "b200_wkv_shift_mix", ptr(h), ptr(shift), ptr(mu), ptr(ctx.token_seq), ptr(ctx.seq_q_start), ptr(ctx.seq_q_len), ptr(ctx.seq_slot),
+        c_int(tokens), c_int(ctx.num_seqs), c_int(hidden), c_int(blends), ptr(out), c_int(dtype_code(h.dtype)), ctx.stream,
+    )
+    ctx.lib.calls += 1  # the slot update is a launch of its own
+    return out
+
+
+def tanh_rows(ctx: StepContext, x: torch.Tensor) -> torch.Tensor:
+    """``x <- tanh(x)`` in place."""
+    _need(x.is_contiguous(), "tanh_rows: a contiguous buffer")
+    ctx.lib.call("b200_tanh_rows", ptr(x), c_int64(x.numel()), c_int(dtype_code(x.dtype)), ctx.stream)
+    return x
+
+
+def wkv_prepare(
+    ctx: StepContext, r: torch.Tensor, k: torch.Tensor, v: torch.Tensor, log_decay: torch.Tensor, w0: torch.Tensor, bonus_w: torch.Tensor,
+    heads: int, dim: int, r32: torch.Tensor, k32: torch.Tensor, v32: torch.Tensor, decay: torch.Tensor, bonus: torch.Tensor,
+) -> None:
+    tokens = r.shape[0]
+    width = heads * dim
+    for tensor in (r, k, v):
+        _need(tuple(tensor.shape) == (tokens, width) and tensor.is_contiguous() and tensor.dtype == r.dtype, "wkv_prepare: bad projections")
+    _need(log_decay.dtype == torch.float32 and tuple(log_decay.shape) == (tokens, width) and log_decay.is_contiguous(), "wkv_prepare: the decay's logarithm is float32")
+    _need(w0.dtype == torch.float32 and w0.numel() == width and bonus_w.dtype == torch.float32 and bonus_w.numel() == width, "wkv_prepare: bad constants")
+    for tensor in (r32, k32, v32, decay):
+        _need(tensor.dtype == torch.float32 and tuple(tensor.shape) == (tokens, width) and tensor.is_contiguous(), "wkv_prepare: bad output")
+    _need(bonus.dtype == torch.float32 and tuple(bonus.shape) == (tokens, heads) and bonus.is_contiguous(), "wkv_prepare: bad bonus output")
+    ctx.lib.call(
+        "b200_wkv_prepare", ptr(r), ptr(k), ptr(v), ptr(log_decay), ptr(w0), ptr(bonus_w), c_int(tokens), c_int(heads), c_int(dim),
+        ptr(r32), ptr(k32), ptr(v32), ptr(decay), ptr(bonus), c_int(dtype_code(r.dtype)), ctx.stream,
+    )
+
+
+def wkv_recurrence(
+    ctx: StepContext, r: torch.Tensor, k: torch.Tensor, v: torch.Tensor, bonus: torch.Tensor, decay: torch.Tensor, state: torch.Tensor,
+    out: torch.Tensor, heads: int, dk: int, dv: int,
+) -> torch.Tensor:
+    _need(state.dtype == torch.float32 and tuple(state.shape[1:]) == (heads, dk, dv) and state.is_contiguous(), "wkv_recurrence: the state is float32 [slots, heads, dk, dv]")
+    _need(out.dtype == torch.float32 and tuple(out.shape) == (r.shape[0], heads * dv) and out.is_contiguous(), "wkv_recurrence: bad output")
+    ctx.lib.call(
+        "b200_wkv_recurrence", ptr(r), ptr(k), ptr(v), ptr(bonus), ptr(decay), ptr(ctx.seq_q_start), ptr(ctx.seq_q_len), ptr(ctx.seq_slot),
+        c_int(ctx.num_seqs), c_int(heads), c_int(dk), c_int(dv), ptr(state), ptr(out), ctx.stream,
+    )
+    return out
+
+
+def wkv_output(ctx: StepContext, o: torch.Tensor, weight: torch.Tensor, gate: torch.Tensor, heads: int, dv: int, eps: float, out: torch.Tensor) -> torch.Tensor:
+    """``out[t, h] = o[t, h] / rms(o[t, h]) * weight[h] * silu(gate[t, h])``."""
+    rows = o.shape[0]
+    _need(o.dtype == torch.float32 and o.is_contiguous() and tuple(out.shape) == (rows, heads * dv) and out.is_contiguous(), "wkv_output: bad operands")
+    _need(tuple(gate.shape) == (rows, heads * dv) and gate.is_contiguous() and gate.dtype == out.dtype, "wkv_output: bad gate")
+    _need(weight.dtype == torch.float32 and weight.numel() == heads * dv, "wkv_output: weight must be float32 [heads * dv]")
+    ctx.lib.call(
+        "b200_wkv_output", ptr(o), ptr(weight), ptr(gate), c_int(rows), c_int(heads), c_int(dv), c_float(eps), ptr(out),
+        c_int(dtype_code(out.dtype)), ctx.stream,
+    )
+    return out
+
+
+# -- attention without position encoding: unit-RMS queries and keys, blended values, a gate per head -----
+
+
+def norm_kv_write(
+    ctx: StepContext, cache: CacheView, proj: torch.Tensor, q_out: torch.Tensor, q_heads: int, kv_heads: int, dim: int, vdim: int,
+    row_dim: int, normalise: bool, eps: float, shared_values: torch.Tensor | None = None, blend: torch.Tensor | None = None,
+    publish: bool = False,
+) -> torch.Tensor:
+    """Per token of ``proj`` (rows ``[q | k | v | ...]``): queries and keys divided by their root mean square
+    per head (if ``normalise``), queries to ``q_out`` and keys and values to the token's page, all in rows
+    of ``row_dim`` numbers padded with zeros. ``publish``: the raw values also go to ``shared_values``;
+    ``blend`` (one float32 on the device): values become ``(1 - blend) v + blend * shared_values``."""
+    tokens, ld = proj.shape
+    _need(proj.is_contiguous() and cache.keys.dtype == proj.dtype and cache.values is not None, "norm_kv_write: bad operands")
+    _need(tuple(q_out.shape) == (tokens, q_heads * row_dim) and q_out.is_contiguous() and q_out.dtype == proj.dtype, "norm_kv_write: bad q_out")
+    _need(tuple(cache.keys.shape[1:]) == (kv_heads, cache.page_size, row_dim), "norm_kv_write: the cache rows differ from the padded head size")
+    mode = 1 if publish else (2 if blend is not None else 0)
+    if mode:
+        _need(shared_values is not None and tuple(shared_values.shape) == (tokens, kv_heads * vdim) and shared_values.dtype == proj.dtype and shared_values.is_contiguous(), "norm_kv_write: bad shared values")
+        _need(blend is None or (blend.dtype == torch.float32 and blend.numel() == 1), "norm_kv_write: the blend factor is one float32")
+    ctx.lib.call(
+        "b200_norm_kv_write", ptr(proj), c_int(ld), ptr(ctx.positions), ptr(ctx.token_seq), ptr(ctx.seq_kv_len), ptr(cache.block_table),
+        c_int(cache.max_pages), c_int(cache.num_pages), ptr(cache.keys), ptr(cache.values), ptr(q_out), ptr(shared_values if mode else None),
+        ptr(blend if mode == 2 else None), c_int(mode), c_int(tokens), c_int(q_heads), c_int(kv_heads), c_int(dim), c_int(vdim),
+        c_int(row_dim), c_int(cache.page_size), c_int(1 if normalise else 0), c_float(eps), c_int(1 if cache.writes else 0),
+        c_int(dtype_code(proj.dtype)), ptr(ctx.err), ctx.stream,
+    )
+    return q_out
+
+
+def head_gate(ctx: StepContext, attn: torch.Tensor, proj: torch.Tensor | None, gate_offset: int, heads: int, vdim: int, row_dim: int, out: torch.Tensor) -> torch.Tensor:
+    """``out[t, h, :] = attn[t, h, :vdim] * sigmoid(proj[t, gate_offset + h])`` (``proj`` None: no gate; the
+    kernel then only drops the padding)."""
+    tokens = attn.shape[0]
+    _need(tuple(attn.shape) == (tokens, heads * row_dim) and attn.is_contiguous() and tuple(out.shape) == (tokens, heads * vdim) and out.is_contiguous() and out.dtype == attn.dtype, "head_gate: bad operands")
+    _need(proj is None or (proj.is_contiguous() and proj.dtype == attn.dtype and proj.shape[1] >= gate_offset + heads), "head_gate: bad gate logits")
+    ctx.lib.call(
+        "b200_head_gate", ptr(attn), ptr(proj), c_int(proj.shape[1] if proj is not None else 0), c_int(gate_offset), c_int(tokens), c_int(heads),
+        c_int(vdim), c_int(row_dim), ptr(out), c_int(dtype_code(attn.dtype)), ctx.stream,
+    )
+    return out
+
+
+# -- the routed feed-forward --------------------------------------------------------------------------------
+
+
+def moe_route(ctx: StepContext, logits: torch.Tensor, groups: int, keep: int, top: int, scale: float, ids: torch.Tensor, weights: torch.Tensor) -> None:
+    tokens, experts = logits.shape
+    _need(logits.dtype == torch.float32 and logits.is_contiguous(), "moe_route: router logits are contiguous float32")
+    _need(ids.dtype == torch.int32 and tuple(ids.shape) == (tokens, top) and ids.is_contiguous(), "moe_route: bad ids")
+    _need(weights.dtype == torch.float32 and tuple(weights.shape) == (tokens, top) and weights.is_contiguous(), "moe_route: bad weights")
+    ctx.lib.call(
+        "b200_moe_route", ptr(logits), c_int(tokens), c_int(experts), c_int(groups), c_int(keep), c_int(top), c_float(scale), ptr(ids),
+        ptr(weights), ctx.stream,
+    )
+
+
+def moe_tile_rows(ctx: StepContext) -> int:
+    return int(ctx.lib.lib.b200_moe_tile_rows())
+
+
+def moe_experts(
+    ctx: StepContext, h: torch.Tensor, ids: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, limit: float, out: torch.Tensor
+) -> torch.Tensor:
+    """``out[t * top + j] = expert ids[t, j] applied to h[t]`` (float32, not yet weighted). ``w_gate_up`` is
+    ``[experts, 2 * ff, width]`` (gate rows, then up rows), ``w_down`` ``[experts, width, ff]``. Three launches:
+    the slots are sorted by expert into runs of whole tiles, then the two products walk the tiles."""
+    tokens, width = h.shape
+    top = ids.shape[1]
+    experts, twice, _ = w_gate_up.shape
+    ff = twice // 2
+    slots = tokens * top
+    _need(h.is_contiguous() and w_gate_up.is_contiguous() and w_down.is_contiguous() and w_gate_up.dtype == h.dtype and w_down.dtype == h.dtype, "moe_experts: bad operands")
+    _need(tuple(w_gate_up.shape) == (experts, 2 * ff, width) and tuple(w_down.shape) == (experts, width, ff), "moe_experts: bad weights")
+    _need(out.dtype == torch.float32 and tuple(out.shape) == (slots, width) and out.is_contiguous(), "moe_experts: bad output")
+    tile = moe_tile_rows(ctx)
+    max_tiles = (slots + experts * (tile - 1)) // tile + 1
+    capacity = max_tiles * tile
+    place_slot = ctx.buffer("moe_place_slot", (capacity,), torch.int32, per_token=False)
+    tile_expert = ctx.buffer("moe_tile_expert", (max_tiles + 1,), torch.int32, per_token=False)
+    act = ctx.buffer("moe_act", (capacity, ff), per_token=False)
+    num_tiles = tile_expert[max_tiles:]
+    ctx.lib.call("b200_moe_sort", ptr(ids), c_int(slots), c_int(experts), c_int(capacity), ptr(place_slot), ptr(tile_expert), ptr(num_tiles), ctx.stream)
+    code = c_int(dtype_code(h.dtype))
+    ctx.lib.call(
+        "b200_moe_gate_up", ptr(h), ptr(w_gate_up), ptr(place_slot), ptr(tile_expert), ptr(num_tiles), c_int(max_tiles), c_int(top),
+        c_int(width), c_int(ff), c_float(limit), ptr(act), code, ctx.stream,
+    )
+    ctx.lib.call(
+        "b200_moe_down", ptr(act), ptr(w_down), ptr(place_slot), ptr(tile_expert), ptr(num_tiles), c_int(max_tiles), c_int(width), c_int(ff),
+        ptr(out), code, ctx.stream,
+    )
+    return out
+
+
+def moe_combine(ctx: StepContext, expert_out: torch.Tensor, weights: torch.Tensor, shared: torch.Tensor | None, out: torch.Tensor) -> torch.Tensor:
+    tokens, top = weights.shape
+    width = out.shape[1]
+    _need(expert_out.dtype == torch.float32 and tuple(expert_out.shape) == (tokens * top, width) and expert_out.is_contiguous(), "moe_combine: bad expert outputs")
+    _need(out.is_contiguous() and out.shape[0] == tokens and (shared is None or (shared.shape == out.shape and shared.dtype == out.dtype and shared.is_contiguous())), "moe_combine: bad operands")
+    ctx.lib.call(
+        "b200_moe_combine", ptr(expert_out), ptr(weights), ptr(shared), c_int(tokens), c_int(top), c_int(width), ptr(out),
+        c_int(dtype_code(out.dtype)), ctx.stream,
+    )
+    return out
+
+
+def clamped_glu(ctx: StepContext, gate_up: torch.Tensor, limit: float, out: torch.Tensor) -> torch.Tensor:
+    """``out = g * sigmoid(1.702 g) * (u + 1)`` with ``g = min(gate, limit)``, ``u = clamp(up, -limit, limit)``; rows of
+    ``gate_up`` are ``[gate | up]``."""
+    rows, twice = gate_up.shape
+    ff = twice // 2
+    _need(twice == 2 * ff and tuple(out.shape) == (rows, ff) and gate_up.is_contiguous() and out.is_contiguous() and out.dtype == gate_up.dtype, "clamped_glu: bad operands")
+    ctx.lib.call("b200_clamped_glu", ptr(gate_up), c_int(rows), c_int(ff), c_float(limit), ptr(out), c_int(dtype_code(out.dtype)), ctx.stream)
+    return out

@@ -140,7 +140,9 @@ class RoutedExperts(Part):
     def forward(self, ctx: StepContext, h: torch.Tensor) -> torch.Tensor:
         t, width = ctx.num_tokens, self.hidden_size
         logits = ops.linear(ctx, h, self.w_router, ctx.buffer("moe_logits", (t, self.experts), torch.float32))
-        ids = ctx.buffer("moe_ids", (t, self.top), torch.int32)
+        # Every routed layer keeps the step's choices in a buffer of its own, so that they can be read after
+        # the step (expert load statistics, tests), also when the step was replayed from a captured graph.
+        ids = ctx.buffer("moe_ids:" + self.prefix, (t, self.top), torch.int32)
         weights = ctx.buffer("moe_weights", (t, self.top), torch.float32)
         ops.moe_route(ctx, logits, self.group_count, self.group_keep, self.top, self.route_scale, ids, weights)
         expert_out = ops.moe_experts(

@@ -173,14 +173,35 @@ def route(scores: np.ndarray, top: int, group_count: int, group_keep: int) -> np
     return np.argsort(-masked, kind="stable")[:top]
 
 
-def moe(h: np.ndarray, w: dict, prefix: str, mlp: dict) -> np.ndarray:
+def route_margin(scores: np.ndarray, top: int, group_count: int, group_keep: int) -> float:
+    """How far the choice is from another one: the smaller of the gap between the last kept and the first
+    dropped group's score and the gap between the last chosen and the first unchosen allowed score."""
+    experts = scores.shape[0]
+    size = experts // group_count
+    group_score = np.sort(np.sort(scores.reshape(group_count, size), axis=1)[:, -2:].sum(axis=1))[::-1]
+    margin = group_score[group_keep - 1] - group_score[group_keep] if group_keep < group_count else np.inf
+    chosen = set(route(scores, experts, group_count, group_keep)[: group_keep * size].tolist())
+    allowed = np.sort(scores[sorted(chosen)])[::-1]
+    if top < len(allowed):
+        margin = min(margin, allowed[top - 1] - allowed[top])
+    return float(margin)
+
+
+def moe(h: np.ndarray, w: dict, prefix: str, mlp: dict, margins: list | None = None, choices=None, free: list | None = None) -> np.ndarray:
+    """``margins`` receives, per token, how close the router's choice was (see :func:`route_margin`) and
+    ``free`` the choice itself; with ``choices`` (``[T, top]``) the experts are those instead, weighted by
+    their own scores as if they had been chosen."""
     h = h.astype(F64)
     router = mlp["router"]
     groups = router.get("groups") or {"count": 1, "keep": 1}
     scores = sigmoid(linear(h, w[prefix + "router"]))
+    if margins is not None:
+        margins.append(np.array([route_margin(row, router["top"], groups["count"], groups["keep"]) for row in scores]))
+    if free is not None:
+        free.append(np.array([route(row, router["top"], groups["count"], groups["keep"]) for row in scores]))
     out = np.zeros((h.shape[0], w[prefix + "e0.down"].shape[0]), F64)
     for t in range(h.shape[0]):
-        chosen = route(scores[t], router["top"], groups["count"], groups["keep"])
+        chosen = route(scores[t], router["top"], groups["count"], groups["keep"]) if choices is None else np.asarray(choices[t], dtype=np.int64)
         weights = scores[t, chosen] / (scores[t, chosen].sum() + 1e-20) * router["scale"]
         for e, weight in zip(chosen, weights):
             out[t] += weight * clamped_expert(h[t : t + 1], w, f"{prefix}e{e}.", mlp["expert"]["limit"])[0]
@@ -204,9 +225,12 @@ class Sequence:
         self.layers: dict[int, object] = {}
 
 
-def forward(config: dict, w: dict, tokens, seq: Sequence | None = None, layer_sums: list | None = None) -> np.ndarray:
+def forward(config: dict, w: dict, tokens, seq: Sequence | None = None, layer_sums: list | None = None, margins: list | None = None,
+            choices: dict | None = None, free: list | None = None) -> np.ndarray:
     """Feeds ``tokens`` as the next tokens of ``seq`` (a fresh sequence if None); returns logits ``[T, vocab]``.
-    ``layer_sums`` receives the sum of the streams after every layer."""
+    ``layer_sums`` receives the sum of the streams after every layer, ``margins`` and ``free`` one array per
+    routed layer with every token's distance from another choice of experts and the choice; ``choices``
+    (layer index -> ``[T, top]``) replaces the routers' choices."""
     seq = Sequence() if seq is None else seq
     eps = config["norm"]["eps"]
     n = int(config.get("streams", 1))
@@ -242,9 +266,17 @@ def forward(config: dict, w: dict, tokens, seq: Sequence | None = None, layer_su
 
         xs = sublayer(xs, prefix, 1, mixer)
         if layer.get("mlp") is not None:
-            xs = sublayer(xs, prefix, 2, lambda h: moe(h, w, prefix + "mlp.", layer["mlp"]))
+            xs = sublayer(xs, prefix, 2, lambda h: moe(h, w, prefix + "mlp.", layer["mlp"], margins, None if choices is None else choices[index], free))
         if layer_sums is not None:
             layer_sums.append(xs.sum(axis=0))
     seq.length += len(tokens)
     h = rms_norm(xs.sum(axis=0), w["final.norm"], eps)
     return softcap(linear(h, w["head"]), config["logit_softcap"])
+
+
+def greedy(config: dict, w: dict, prompt, count: int) -> list[int]:
+    """``count`` tokens by arg-max, each from a forward pass over everything so far."""
+    tokens = list(prompt)
+    for _ in range(count):
+        tokens.append(int(np.argmax(forward(config, w, tokens)[-1])))
+    return tokens[len(prompt):]

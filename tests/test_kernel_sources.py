@@ -21,6 +21,8 @@ BEFORE_THE_CHAIN = {
     "W", "table", "weight", "bias", "inv_freq", "positions", "token_seq", "seq_kv_len", "block_table",
     # weights and constants of the post-norm blocks, the latent attention and the delta rule
     "scale", "mix", "coefficients", "norm_weight", "sink", "taps_w", "a_log", "dt_bias",
+    # stream weights of the hyper-connections, blend factors, decay offset and bonus of the recurrent mixer with a bonus
+    "mix_w", "out_w", "in_w", "mu", "w0", "u",
 }
 
 

@@ -291,6 +291,30 @@ def gunedra_shape(width: int) -> dict:
     }
 
 
+def tunadra_shape(width: int) -> dict:
+    """Layer sizes in the proportions of a real model of this design: attention heads of 128 sharing
+    key/value heads as the Qwen2 shape does, recurrent heads of 64 x 64, three streams, and a routed
+    feed-forward of 32 experts (four groups, two kept, four experts per token) plus a shared expert, sized
+    so that a token passes through as many feed-forward weights as in the dense shape of this width."""
+    heads, ff = DESIGN_SIZES[width]
+    mlp = {
+        "kind": "moe", "expert": {"ff": ff // 8, "limit": 7.0}, "shared": {"ff": ff // 2, "limit": 7.0},
+        "router": {"experts": 32, "top": 4, "scale": 2.5, "groups": {"count": 4, "keep": 2}},
+    }
+    attention = {
+        "type": "attention", "mlp": mlp,
+        "mixer": {"heads": heads, "kv_heads": max(1, heads // 6), "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "v_mix": True},
+    }
+    recurrent = {"type": "wkv", "mlp": mlp, "mixer": {"heads": width // 64, "dim": 64, "decay_rank": 64}}
+    return {
+        "architecture": "Tunadra", "vocab": DESIGN_VOCAB, "width": width, "streams": 3, "logit_softcap": 30.0,
+        "embedding": {"scale": width ** 0.5}, "norm": {"eps": 1e-5}, "layers": [attention, attention, recurrent, attention][:DESIGN_LAYERS],
+    }
+
+
+DESIGN_SHAPES = {"gunedra": gunedra_shape, "tunadra": tunadra_shape}
+
+
 def qwen2_shape(width: int) -> dict:
     heads, ff = DESIGN_SIZES[width]
     return dict(MODEL, num_hidden_layers=DESIGN_LAYERS, hidden_size=width, num_attention_heads=heads,
@@ -322,7 +346,7 @@ def compare_designs(args) -> int:
     batch = args.batch
     results = {}
     for width in [int(w) for w in args.design_sizes.split(",")]:
-        for design, raw in (("gunedra", gunedra_shape(width)), ("qwen2", qwen2_shape(width))):
+        for design, raw in ((args.design, DESIGN_SHAPES[args.design](width)), ("qwen2", qwen2_shape(width))):
             _, config = parse_config(raw)
             model = random_model(config, seed=0, dtype="bfloat16", device="cuda:0")
             engine = Engine(model=model, max_num_sequences=max(batch, 8), max_model_length=CONTEXT, num_pages=(batch + 2) * CONTEXT // PAGE,
@@ -416,7 +440,7 @@ def compare_designs(args) -> int:
             del engine, runner, cache, model
             torch.cuda.empty_cache()
     print(json.dumps({
-        "designs": results, "batch": batch, "prompt_len": PROMPT, "dtype": "bf16", "peaks": peak,
+        "designs": results, "design": args.design, "batch": batch, "prompt_len": PROMPT, "dtype": "bf16", "peaks": peak,
         "data": "synthetic: seeded random weights N(0,0.02), token ids uniform in the vocabulary",
     }))
     return 0
@@ -457,9 +481,10 @@ def main() -> int:
     parser.add_argument("--decode-kernel", choices=["chain", "resident"], default="chain",
                         help="'resident': time the one-kernel decode step instead of the chain of kernels")
     parser.add_argument("--designs", action="store_true",
-                        help="instead of the headline run: prefill and decode of the Gunedra design beside the Qwen2 shape of "
+                        help="instead of the headline run: prefill and decode of another design (--design) beside the Qwen2 shape of "
                         "equal width, feed-forward and head count, at a few layer sizes, with each kernel's time")
     parser.add_argument("--design-sizes", default="1536,3584", help="widths for --designs (1536, 3584 or 5120)")
+    parser.add_argument("--design", choices=["gunedra", "tunadra"], default="gunedra", help="which design --designs puts beside the Qwen2 shape")
     args = parser.parse_args()
     if args.impl == "reference":
         return reference_arm(args)

@@ -251,6 +251,167 @@ moe_down_kernel(const T* act, const T* __restrict__ weight, const int* place_slo
   }
 }
 
+// The same two products on tensor cores (bfloat16 operands, 32-bit sums): a block takes one tile of
+// kTileM sorted places and kMmaN output columns of each of its MATS matrices (2: gate and up with the
+// activation as epilogue; 1: down) and walks K in steps of kMmaK through two cp.async stages; four
+// warps own 16 columns each; fragments by ldmatrix, `mma.sync` m16n8k16. A row's sums depend on the
+// row, the weights and K only (a fixed order of k steps), not on the other rows of the tile. Rows of A
+// start at `a_rows[r]` (null: zeros); K must be a multiple of 8 (16-byte copies).
+constexpr int kMmaN = 64;
+constexpr int kMmaK = 32;
+constexpr int kMmaPitch = kMmaK + 8;  // 80 bytes a row: ldmatrix reads without bank conflicts
+constexpr int kMmaThreads = 128;
+
+__device__ __forceinline__ void copy16(void* smem, const void* gmem, bool valid) {
+  const uint32_t s = static_cast<uint32_t>(__cvta_generic_to_shared(smem));
+  const int bytes = valid ? 16 : 0;
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(s), "l"(gmem), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void ldmatrix4(uint32_t (&r)[4], const void* smem) {
+  const uint32_t s = static_cast<uint32_t>(__cvta_generic_to_shared(smem));
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
+}
+__device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+// acc[mat][m tile][n tile][4] for the block's tile; `b_rows[mat]` is row n0 of matrix `mat` ([.][K], K contiguous),
+// `n_valid` how many of the kMmaN rows exist.
+template <int MATS>
+__device__ __forceinline__ void tile_product(const __nv_bfloat16* const* a_rows, const __nv_bfloat16* const (&b_rows)[MATS], int n_valid, int K,
+                                             __nv_bfloat16 (*a_smem)[kTileM][kMmaPitch], __nv_bfloat16 (*b_smem)[MATS][kMmaN][kMmaPitch],
+                                             float (&acc)[MATS][2][2][4]) {
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+#pragma unroll
+  for (int mat = 0; mat < MATS; ++mat)
+#pragma unroll
+    for (int m = 0; m < 2; ++m)
+#pragma unroll
+      for (int n = 0; n < 2; ++n)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) acc[mat][m][n][i] = 0.f;
+  auto fetch = [&](int stage, int k0) {
+    {  // A: kTileM rows x 4 chunks of 8 = 128 chunks, one per thread
+      const int r = tid >> 2, c = (tid & 3) * 8;
+      const __nv_bfloat16* src = a_rows[r];
+      const bool in = src != nullptr && k0 + c < K;
+      copy16(&a_smem[stage][r][c], in ? src + k0 + c : b_rows[0], in);
+    }
+#pragma unroll
+    for (int mat = 0; mat < MATS; ++mat)
+#pragma unroll
+      for (int i = 0; i < kMmaN * 4 / kMmaThreads; ++i) {
+        const int chunk = tid + i * kMmaThreads;
+        const int r = chunk >> 2, c = (chunk & 3) * 8;
+        const bool in = r < n_valid && k0 + c < K;
+        copy16(&b_smem[stage][mat][r][c], in ? b_rows[mat] + static_cast<int64_t>(r) * K + k0 + c : b_rows[0], in);
+      }
+  };
+  const int steps = (K + kMmaK - 1) / kMmaK;
+  fetch(0, 0);
+  asm volatile("cp.async.commit_group;" ::: "memory");
+  for (int step = 0; step < steps; ++step) {
+    const int stage = step & 1;
+    if (step + 1 < steps) fetch(stage ^ 1, (step + 1) * kMmaK);
+    asm volatile("cp.async.commit_group;" ::: "memory");
+    asm volatile("cp.async.wait_group 1;" ::: "memory");
+    __syncthreads();
+#pragma unroll
+    for (int kk = 0; kk < kMmaK; kk += 16) {
+      uint32_t a[2][4];
+#pragma unroll
+      for (int m = 0; m < 2; ++m) ldmatrix4(a[m], &a_smem[stage][m * 16 + (lane & 7) + ((lane >> 3) & 1) * 8][kk + (lane >> 4) * 8]);
+#pragma unroll
+      for (int mat = 0; mat < MATS; ++mat) {
+        uint32_t b[4];  // two n8 tiles: (b0, b1) of columns 0..7 and of columns 8..15 of the warp's 16
+        ldmatrix4(b, &b_smem[stage][mat][warp * 16 + (lane & 7) + (lane >> 4) * 8][kk + ((lane >> 3) & 1) * 8]);
+#pragma unroll
+        for (int m = 0; m < 2; ++m) {
+          mma_bf16(acc[mat][m][0], a[m], b[0], b[1]);
+          mma_bf16(acc[mat][m][1], a[m], b[2], b[3]);
+        }
+      }
+    }
+    __syncthreads();
+  }
+  asm volatile("cp.async.wait_group 0;" ::: "memory");
+}
+
+__global__ void __launch_bounds__(kMmaThreads)
+moe_gate_up_mma_kernel(const __nv_bfloat16* h, const __nv_bfloat16* __restrict__ weight, const int* place_slot, const int* tile_expert,
+                       const int* num_tiles, int top, int width, int ff, float limit, __nv_bfloat16* act) {
+  __shared__ __align__(16) __nv_bfloat16 a_smem[2][kTileM][kMmaPitch];
+  __shared__ __align__(16) __nv_bfloat16 b_smem[2][2][kMmaN][kMmaPitch];
+  __shared__ const __nv_bfloat16* a_rows[kTileM];
+  wait_for_predecessor();
+  let_successor_start();
+  const int tile = blockIdx.x;
+  if (tile >= *num_tiles) return;
+  const int expert = tile_expert[tile];
+  const int n0 = blockIdx.y * kMmaN;
+  if (threadIdx.x < kTileM) {
+    const int slot = place_slot[tile * kTileM + threadIdx.x];
+    a_rows[threadIdx.x] = slot < 0 ? nullptr : h + static_cast<int64_t>(slot / top) * width;
+  }
+  __syncthreads();
+  const __nv_bfloat16* wg = weight + (static_cast<int64_t>(expert) * 2 * ff + n0) * width;
+  const __nv_bfloat16* const b_rows[2] = {wg, wg + static_cast<int64_t>(ff) * width};
+  float acc[2][2][2][4];
+  tile_product<2>(a_rows, b_rows, min(kMmaN, ff - n0), width, a_smem, b_smem, acc);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+  for (int m = 0; m < 2; ++m)
+#pragma unroll
+    for (int n = 0; n < 2; ++n)
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        const int r = m * 16 + (lane >> 2) + half * 8;
+        const int col = n0 + warp * 16 + n * 8 + (lane & 3) * 2;
+        if (a_rows[r] == nullptr || col >= ff) continue;  // ff is even: the pair is whole
+        const float y0 = clamped_glu(acc[0][m][n][half * 2], acc[1][m][n][half * 2], limit);
+        const float y1 = clamped_glu(acc[0][m][n][half * 2 + 1], acc[1][m][n][half * 2 + 1], limit);
+        *reinterpret_cast<__nv_bfloat162*>(act + (static_cast<int64_t>(tile) * kTileM + r) * ff + col) = __floats2bfloat162_rn(y0, y1);
+      }
+}
+
+__global__ void __launch_bounds__(kMmaThreads)
+moe_down_mma_kernel(const __nv_bfloat16* act, const __nv_bfloat16* __restrict__ weight, const int* place_slot, const int* tile_expert,
+                    const int* num_tiles, int width, int ff, float* out) {
+  __shared__ __align__(16) __nv_bfloat16 a_smem[2][kTileM][kMmaPitch];
+  __shared__ __align__(16) __nv_bfloat16 b_smem[2][1][kMmaN][kMmaPitch];
+  __shared__ const __nv_bfloat16* a_rows[kTileM];
+  __shared__ int row_slot[kTileM];
+  wait_for_predecessor();
+  let_successor_start();
+  const int tile = blockIdx.x;
+  if (tile >= *num_tiles) return;
+  const int expert = tile_expert[tile];
+  const int n0 = blockIdx.y * kMmaN;
+  if (threadIdx.x < kTileM) {
+    const int slot = place_slot[tile * kTileM + threadIdx.x];
+    row_slot[threadIdx.x] = slot;
+    a_rows[threadIdx.x] = slot < 0 ? nullptr : act + (static_cast<int64_t>(tile) * kTileM + threadIdx.x) * ff;
+  }
+  __syncthreads();
+  const __nv_bfloat16* const b_rows[1] = {weight + (static_cast<int64_t>(expert) * width + n0) * ff};
+  float acc[1][2][2][4];
+  tile_product<1>(a_rows, b_rows, min(kMmaN, width - n0), ff, a_smem, b_smem, acc);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+  for (int m = 0; m < 2; ++m)
+#pragma unroll
+    for (int n = 0; n < 2; ++n)
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        const int r = m * 16 + (lane >> 2) + half * 8;
+        const int col = n0 + warp * 16 + n * 8 + (lane & 3) * 2;
+        if (row_slot[r] < 0 || col >= width) continue;  // width is even: the pair is whole
+        *reinterpret_cast<float2*>(out + static_cast<int64_t>(row_slot[r]) * width + col) = make_float2(acc[0][m][n][half * 2], acc[0][m][n][half * 2 + 1]);
+      }
+}
+
 // out[t] = sum_j weights[t][j] * expert_out[t * top + j] (+ shared[t]), in the order of j.
 template <typename T>
 __global__ void moe_combine_kernel(const float* expert_out, const float* weights, const T* shared, int top, int width, T* out) {
@@ -276,6 +437,30 @@ __global__ void clamped_glu_kernel(const T* gate_up, int64_t rows, int ff, float
     const int64_t r = idx / ff;
     const int c = static_cast<int>(idx % ff);
     out[idx] = from_f32<T>(clamped_glu(to_f32<T>(gate_up[r * 2 * ff + c]), to_f32<T>(gate_up[r * 2 * ff + ff + c]), limit));
+  }
+}
+
+// The same for bfloat16 rows whose halves start on 16-byte boundaries (ff a multiple of 8): eight outputs a thread.
+__global__ void clamped_glu_wide_kernel(const __nv_bfloat16* gate_up, int64_t rows, int ff, float limit, __nv_bfloat16* out) {
+  wait_for_predecessor();
+  let_successor_start();
+  const int chunks = ff / 8;
+  const int64_t total = rows * chunks;
+  for (int64_t idx = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; idx < total; idx += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int64_t r = idx / chunks;
+    const int c = static_cast<int>(idx % chunks) * 8;
+    const uint4 graw = *reinterpret_cast<const uint4*>(gate_up + r * 2 * ff + c);
+    const uint4 uraw = *reinterpret_cast<const uint4*>(gate_up + r * 2 * ff + ff + c);
+    const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&graw);
+    const __nv_bfloat162* u2 = reinterpret_cast<const __nv_bfloat162*>(&uraw);
+    uint4 packed;
+    __nv_bfloat162* y2 = reinterpret_cast<__nv_bfloat162*>(&packed);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 g = __bfloat1622float2(g2[j]), u = __bfloat1622float2(u2[j]);
+      y2[j] = __floats2bfloat162_rn(clamped_glu(g.x, u.x, limit), clamped_glu(g.y, u.y, limit));
+    }
+    *reinterpret_cast<uint4*>(out + r * ff + c) = packed;
   }
 }
 
@@ -309,8 +494,12 @@ B200_API int b200_moe_sort(const int* ids, int slots, int experts, int capacity,
   return b200_check_launch("moe_sort");
 }
 
+static bool aligned16(const void* p) { return reinterpret_cast<uintptr_t>(p) % 16 == 0; }
+
+// `use_mma`: bfloat16 on tensor cores where the sizes allow (K a multiple of 8); 0 keeps the plain kernel.
 B200_API int b200_moe_gate_up(const void* h, const void* weight, const int* place_slot, const int* tile_expert, const int* num_tiles,
-                              int max_tiles, int top, int width, int ff, float limit, void* act, int dtype, cudaStream_t stream) {
+                              int max_tiles, int top, int width, int ff, float limit, void* act, int dtype, int use_mma,
+                              cudaStream_t stream) {
   if (max_tiles == 0) return 0;
   B200_REQUIRE(max_tiles > 0 && top > 0 && width > 0 && ff > 0 && limit > 0.f, "moe_gate_up: bad sizes");
   const dim3 grid(max_tiles, (ff + kTileN - 1) / kTileN);
@@ -318,6 +507,11 @@ B200_API int b200_moe_gate_up(const void* h, const void* weight, const int* plac
   if (dtype == DTYPE_F32) {
     launch_kernel(moe_gate_up_kernel<float>, grid, dim3(kGemmThreads), 0, stream, static_cast<const float*>(h),
                   static_cast<const float*>(weight), place_slot, tile_expert, num_tiles, top, width, ff, limit, static_cast<float*>(act));
+  } else if (dtype == DTYPE_BF16 && use_mma && width % 8 == 0 && ff % 8 == 0 && aligned16(h) && aligned16(weight) && aligned16(act)) {
+    const dim3 mma_grid(max_tiles, (ff + kMmaN - 1) / kMmaN);
+    launch_kernel(moe_gate_up_mma_kernel, mma_grid, dim3(kMmaThreads), 0, stream, static_cast<const __nv_bfloat16*>(h),
+                  static_cast<const __nv_bfloat16*>(weight), place_slot, tile_expert, num_tiles, top, width, ff, limit,
+                  static_cast<__nv_bfloat16*>(act));
   } else if (dtype == DTYPE_BF16) {
     launch_kernel(moe_gate_up_kernel<__nv_bfloat16>, grid, dim3(kGemmThreads), 0, stream, static_cast<const __nv_bfloat16*>(h),
                   static_cast<const __nv_bfloat16*>(weight), place_slot, tile_expert, num_tiles, top, width, ff, limit,
@@ -329,7 +523,7 @@ B200_API int b200_moe_gate_up(const void* h, const void* weight, const int* plac
 }
 
 B200_API int b200_moe_down(const void* act, const void* weight, const int* place_slot, const int* tile_expert, const int* num_tiles,
-                           int max_tiles, int width, int ff, float* out, int dtype, cudaStream_t stream) {
+                           int max_tiles, int width, int ff, float* out, int dtype, int use_mma, cudaStream_t stream) {
   if (max_tiles == 0) return 0;
   B200_REQUIRE(max_tiles > 0 && width > 0 && ff > 0, "moe_down: bad sizes");
   const dim3 grid(max_tiles, (width + kTileN - 1) / kTileN);
@@ -337,6 +531,10 @@ B200_API int b200_moe_down(const void* act, const void* weight, const int* place
   if (dtype == DTYPE_F32) {
     launch_kernel(moe_down_kernel<float>, grid, dim3(kGemmThreads), 0, stream, static_cast<const float*>(act),
                   static_cast<const float*>(weight), place_slot, tile_expert, num_tiles, width, ff, out);
+  } else if (dtype == DTYPE_BF16 && use_mma && width % 8 == 0 && ff % 8 == 0 && aligned16(act) && aligned16(weight) && aligned16(out)) {
+    const dim3 mma_grid(max_tiles, (width + kMmaN - 1) / kMmaN);
+    launch_kernel(moe_down_mma_kernel, mma_grid, dim3(kMmaThreads), 0, stream, static_cast<const __nv_bfloat16*>(act),
+                  static_cast<const __nv_bfloat16*>(weight), place_slot, tile_expert, num_tiles, width, ff, out);
   } else if (dtype == DTYPE_BF16) {
     launch_kernel(moe_down_kernel<__nv_bfloat16>, grid, dim3(kGemmThreads), 0, stream, static_cast<const __nv_bfloat16*>(act),
                   static_cast<const __nv_bfloat16*>(weight), place_slot, tile_expert, num_tiles, width, ff, out);
@@ -373,6 +571,10 @@ B200_API int b200_clamped_glu(const void* gate_up, int rows, int ff, float limit
   if (dtype == DTYPE_F32) {
     launch_kernel(clamped_glu_kernel<float>, grid, dim3(threads), 0, stream, static_cast<const float*>(gate_up), static_cast<int64_t>(rows),
                   ff, limit, static_cast<float*>(out));
+  } else if (dtype == DTYPE_BF16 && ff % 8 == 0 && aligned16(gate_up) && aligned16(out)) {
+    const int64_t wide = (total / 8 + threads - 1) / threads;
+    launch_kernel(clamped_glu_wide_kernel, dim3(static_cast<unsigned>(wide < 65535 ? wide : 65535)), dim3(threads), 0, stream,
+                  static_cast<const __nv_bfloat16*>(gate_up), static_cast<int64_t>(rows), ff, limit, static_cast<__nv_bfloat16*>(out));
   } else if (dtype == DTYPE_BF16) {
     launch_kernel(clamped_glu_kernel<__nv_bfloat16>, grid, dim3(threads), 0, stream, static_cast<const __nv_bfloat16*>(gate_up),
                   static_cast<int64_t>(rows), ff, limit, static_cast<__nv_bfloat16*>(out));

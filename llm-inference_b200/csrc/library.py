@@ -98,8 +98,8 @@ _SIGNATURES: dict[str, list] = {
     "b200_head_gate": [c_void_p, c_void_p] + [c_int] * 6 + [c_void_p, c_int, c_void_p],
     "b200_moe_route": [c_void_p] + [c_int] * 5 + [c_float, c_void_p, c_void_p, c_void_p],
     "b200_moe_sort": [c_void_p, c_int, c_int, c_int] + [c_void_p] * 4,
-    "b200_moe_gate_up": [c_void_p] * 5 + [c_int] * 4 + [c_float, c_void_p, c_int, c_void_p],
-    "b200_moe_down": [c_void_p] * 5 + [c_int] * 3 + [c_void_p, c_int, c_void_p],
+    "b200_moe_gate_up": [c_void_p] * 5 + [c_int] * 4 + [c_float, c_void_p, c_int, c_int, c_void_p],
+    "b200_moe_down": [c_void_p] * 5 + [c_int] * 3 + [c_void_p, c_int, c_int, c_void_p],
     "b200_moe_combine": [c_void_p] * 3 + [c_int] * 3 + [c_void_p, c_int, c_void_p],
     "b200_clamped_glu": [c_void_p, c_int, c_int, c_float, c_void_p, c_int, c_void_p],
 }

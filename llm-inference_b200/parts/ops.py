@@ -1004,13 +1004,14 @@ def moe_experts(
     num_tiles = tile_expert[max_tiles:]
     ctx.lib.call("b200_moe_sort", ptr(ids), c_int(slots), c_int(experts), c_int(capacity), ptr(place_slot), ptr(tile_expert), ptr(num_tiles), ctx.stream)
     code = c_int(dtype_code(h.dtype))
+    tensor_cores = c_int(0 if ctx.options.get("moe", "auto") == "plain" else 1)  # bfloat16 only; "plain": the FMA kernels
     ctx.lib.call(
         "b200_moe_gate_up", ptr(h), ptr(w_gate_up), ptr(place_slot), ptr(tile_expert), ptr(num_tiles), c_int(max_tiles), c_int(top),
-        c_int(width), c_int(ff), c_float(limit), ptr(act), code, ctx.stream,
+        c_int(width), c_int(ff), c_float(limit), ptr(act), code, tensor_cores, ctx.stream,
     )
     ctx.lib.call(
         "b200_moe_down", ptr(act), ptr(w_down), ptr(place_slot), ptr(tile_expert), ptr(num_tiles), c_int(max_tiles), c_int(width), c_int(ff),
-        ptr(out), code, ctx.stream,
+        ptr(out), code, tensor_cores, ctx.stream,
     )
     return out
 

@@ -11,7 +11,8 @@
 // output W_down y.
 //
 // Grouping: every (token, choice) pair is a slot. `moe_sort` (one block) counts the slots of each
-// expert, gives each expert a run of whole tiles of kTileM sorted places and writes, per place, the
+// expert, gives each expert a run of whole tiles of `tile_rows` sorted places (kTileM, or four times
+// that for prompt portions on tensor cores) and writes, per place, the
 // slot it holds (-1: padding) and, per tile, its expert. The two product kernels walk tiles: a tile's
 // rows share one expert's weights. Each output number is one thread's sum over K in a fixed order, so
 // a slot's result does not depend on which other slots share its tile, and the final sum over a
@@ -118,7 +119,8 @@ __global__ void moe_route_kernel(const float* z, int tokens, int experts, int gr
 }
 
 // One block. ids [slots]; place_slot [capacity]; tile_expert [max_tiles]; num_tiles [1].
-__global__ void moe_sort_kernel(const int* ids, int slots, int experts, int capacity, int* place_slot, int* tile_expert, int* num_tiles) {
+__global__ void moe_sort_kernel(const int* ids, int slots, int experts, int capacity, int tile_rows, int* place_slot, int* tile_expert,
+                                int* num_tiles) {
   extern __shared__ int sort_smem[];  // counts [experts], cursor [experts]
   int* counts = sort_smem;
   int* cursor = counts + experts;
@@ -135,8 +137,8 @@ __global__ void moe_sort_kernel(const int* ids, int slots, int experts, int capa
   if (threadIdx.x == 0) {
     int tile = 0;
     for (int e = 0; e < experts; ++e) {
-      cursor[e] = tile * kTileM;
-      const int tiles = (counts[e] + kTileM - 1) / kTileM;
+      cursor[e] = tile * tile_rows;
+      const int tiles = (counts[e] + tile_rows - 1) / tile_rows;
       for (int i = 0; i < tiles; ++i) tile_expert[tile + i] = e;
       tile += tiles;
     }
@@ -252,15 +254,25 @@ moe_down_kernel(const T* act, const T* __restrict__ weight, const int* place_slo
 }
 
 // The same two products on tensor cores (bfloat16 operands, 32-bit sums): a block takes one tile of
-// kTileM sorted places and kMmaN output columns of each of its MATS matrices (2: gate and up with the
-// activation as epilogue; 1: down) and walks K in steps of kMmaK through two cp.async stages; four
-// warps own 16 columns each; fragments by ldmatrix, `mma.sync` m16n8k16. A row's sums depend on the
-// row, the weights and K only (a fixed order of k steps), not on the other rows of the tile. Rows of A
-// start at `a_rows[r]` (null: zeros); K must be a multiple of 8 (16-byte copies).
+// 32 * MT sorted places and kMmaN output columns of each of its MATS matrices (2: gate and up with the
+// activation as epilogue; 1: down) and walks K in steps of kMmaK through two cp.async stages;
+// fragments by ldmatrix, `mma.sync` m16n8k16. MT = 1 (steps with few tokens per expert: four warps, 16
+// columns each) or 4 (prompt portions: eight warps as 4 x 2, each 32 rows x 32 columns, so that a
+// weight tile fetched from L2 serves 128 rows). A row's sums depend on the row, the weights and K only
+// (a fixed order of k steps), not on the tile's other rows or on MT. Rows of A start at `a_rows[r]`
+// (null: zeros); K must be a multiple of 8 (16-byte copies).
 constexpr int kMmaN = 64;
 constexpr int kMmaK = 32;
 constexpr int kMmaPitch = kMmaK + 8;  // 80 bytes a row: ldmatrix reads without bank conflicts
-constexpr int kMmaThreads = 128;
+constexpr int kWideTiles = 4;         // MT of the prompt form
+
+template <int MT>
+struct MmaShape {
+  static constexpr int rows = 32 * MT;
+  static constexpr int threads = MT == 1 ? 128 : 256;
+  static constexpr int warps_n = MT == 1 ? 4 : 2;
+  static constexpr int n_tiles = kMmaN / warps_n / 8;  // n8 tiles a warp: 2 or 4
+};
 
 __device__ __forceinline__ void copy16(void* smem, const void* gmem, bool valid) {
   const uint32_t s = static_cast<uint32_t>(__cvta_generic_to_shared(smem));
@@ -277,24 +289,28 @@ __device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], 
                : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
-// acc[mat][m tile][n tile][4] for the block's tile; `b_rows[mat]` is row n0 of matrix `mat` ([.][K], K contiguous),
-// `n_valid` how many of the kMmaN rows exist.
-template <int MATS>
+// acc[mat][m16 tile][n8 tile][4] of this warp's 32 rows (`warp_m`) and columns (`warp_n`); `b_rows[mat]` is row n0
+// of matrix `mat` ([.][K], K contiguous), `n_valid` how many of the kMmaN rows exist.
+template <int MATS, int MT>
 __device__ __forceinline__ void tile_product(const __nv_bfloat16* const* a_rows, const __nv_bfloat16* const (&b_rows)[MATS], int n_valid, int K,
-                                             __nv_bfloat16 (*a_smem)[kTileM][kMmaPitch], __nv_bfloat16 (*b_smem)[MATS][kMmaN][kMmaPitch],
-                                             float (&acc)[MATS][2][2][4]) {
+                                             __nv_bfloat16 (*a_smem)[32 * MT][kMmaPitch], __nv_bfloat16 (*b_smem)[MATS][kMmaN][kMmaPitch],
+                                             float (&acc)[MATS][2][MmaShape<MT>::n_tiles][4]) {
+  using Shape = MmaShape<MT>;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int warp_m = warp / Shape::warps_n, warp_n = warp % Shape::warps_n;
 #pragma unroll
   for (int mat = 0; mat < MATS; ++mat)
 #pragma unroll
     for (int m = 0; m < 2; ++m)
 #pragma unroll
-      for (int n = 0; n < 2; ++n)
+      for (int n = 0; n < Shape::n_tiles; ++n)
 #pragma unroll
         for (int i = 0; i < 4; ++i) acc[mat][m][n][i] = 0.f;
   auto fetch = [&](int stage, int k0) {
-    {  // A: kTileM rows x 4 chunks of 8 = 128 chunks, one per thread
-      const int r = tid >> 2, c = (tid & 3) * 8;
+#pragma unroll
+    for (int i = 0; i < Shape::rows * 4 / Shape::threads; ++i) {
+      const int chunk = tid + i * Shape::threads;
+      const int r = chunk >> 2, c = (chunk & 3) * 8;
       const __nv_bfloat16* src = a_rows[r];
       const bool in = src != nullptr && k0 + c < K;
       copy16(&a_smem[stage][r][c], in ? src + k0 + c : b_rows[0], in);
@@ -302,8 +318,8 @@ __device__ __forceinline__ void tile_product(const __nv_bfloat16* const* a_rows,
 #pragma unroll
     for (int mat = 0; mat < MATS; ++mat)
 #pragma unroll
-      for (int i = 0; i < kMmaN * 4 / kMmaThreads; ++i) {
-        const int chunk = tid + i * kMmaThreads;
+      for (int i = 0; i < kMmaN * 4 / Shape::threads; ++i) {
+        const int chunk = tid + i * Shape::threads;
         const int r = chunk >> 2, c = (chunk & 3) * 8;
         const bool in = r < n_valid && k0 + c < K;
         copy16(&b_smem[stage][mat][r][c], in ? b_rows[mat] + static_cast<int64_t>(r) * K + k0 + c : b_rows[0], in);
@@ -322,91 +338,100 @@ __device__ __forceinline__ void tile_product(const __nv_bfloat16* const* a_rows,
     for (int kk = 0; kk < kMmaK; kk += 16) {
       uint32_t a[2][4];
 #pragma unroll
-      for (int m = 0; m < 2; ++m) ldmatrix4(a[m], &a_smem[stage][m * 16 + (lane & 7) + ((lane >> 3) & 1) * 8][kk + (lane >> 4) * 8]);
+      for (int m = 0; m < 2; ++m)
+        ldmatrix4(a[m], &a_smem[stage][warp_m * 32 + m * 16 + (lane & 7) + ((lane >> 3) & 1) * 8][kk + (lane >> 4) * 8]);
 #pragma unroll
-      for (int mat = 0; mat < MATS; ++mat) {
-        uint32_t b[4];  // two n8 tiles: (b0, b1) of columns 0..7 and of columns 8..15 of the warp's 16
-        ldmatrix4(b, &b_smem[stage][mat][warp * 16 + (lane & 7) + (lane >> 4) * 8][kk + ((lane >> 3) & 1) * 8]);
+      for (int mat = 0; mat < MATS; ++mat)
 #pragma unroll
-        for (int m = 0; m < 2; ++m) {
-          mma_bf16(acc[mat][m][0], a[m], b[0], b[1]);
-          mma_bf16(acc[mat][m][1], a[m], b[2], b[3]);
+        for (int pair = 0; pair < Shape::n_tiles / 2; ++pair) {
+          uint32_t b[4];  // two n8 tiles: (b0, b1) of columns 0..7 and of columns 8..15 of this pair's 16
+          ldmatrix4(b, &b_smem[stage][mat][warp_n * (8 * Shape::n_tiles) + pair * 16 + (lane & 7) + (lane >> 4) * 8][kk + ((lane >> 3) & 1) * 8]);
+#pragma unroll
+          for (int m = 0; m < 2; ++m) {
+            mma_bf16(acc[mat][m][2 * pair], a[m], b[0], b[1]);
+            mma_bf16(acc[mat][m][2 * pair + 1], a[m], b[2], b[3]);
+          }
         }
-      }
     }
     __syncthreads();
   }
   asm volatile("cp.async.wait_group 0;" ::: "memory");
 }
 
-__global__ void __launch_bounds__(kMmaThreads)
+template <int MT>
+__global__ void __launch_bounds__(MmaShape<MT>::threads)
 moe_gate_up_mma_kernel(const __nv_bfloat16* h, const __nv_bfloat16* __restrict__ weight, const int* place_slot, const int* tile_expert,
                        const int* num_tiles, int top, int width, int ff, float limit, __nv_bfloat16* act) {
-  __shared__ __align__(16) __nv_bfloat16 a_smem[2][kTileM][kMmaPitch];
+  using Shape = MmaShape<MT>;
+  __shared__ __align__(16) __nv_bfloat16 a_smem[2][Shape::rows][kMmaPitch];
   __shared__ __align__(16) __nv_bfloat16 b_smem[2][2][kMmaN][kMmaPitch];
-  __shared__ const __nv_bfloat16* a_rows[kTileM];
+  __shared__ const __nv_bfloat16* a_rows[Shape::rows];
   wait_for_predecessor();
   let_successor_start();
   const int tile = blockIdx.x;
   if (tile >= *num_tiles) return;
   const int expert = tile_expert[tile];
   const int n0 = blockIdx.y * kMmaN;
-  if (threadIdx.x < kTileM) {
-    const int slot = place_slot[tile * kTileM + threadIdx.x];
+  if (threadIdx.x < Shape::rows) {
+    const int slot = place_slot[tile * Shape::rows + threadIdx.x];
     a_rows[threadIdx.x] = slot < 0 ? nullptr : h + static_cast<int64_t>(slot / top) * width;
   }
   __syncthreads();
   const __nv_bfloat16* wg = weight + (static_cast<int64_t>(expert) * 2 * ff + n0) * width;
   const __nv_bfloat16* const b_rows[2] = {wg, wg + static_cast<int64_t>(ff) * width};
-  float acc[2][2][2][4];
-  tile_product<2>(a_rows, b_rows, min(kMmaN, ff - n0), width, a_smem, b_smem, acc);
+  float acc[2][2][Shape::n_tiles][4];
+  tile_product<2, MT>(a_rows, b_rows, min(kMmaN, ff - n0), width, a_smem, b_smem, acc);
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int warp_m = warp / Shape::warps_n, warp_n = warp % Shape::warps_n;
 #pragma unroll
   for (int m = 0; m < 2; ++m)
 #pragma unroll
-    for (int n = 0; n < 2; ++n)
+    for (int n = 0; n < Shape::n_tiles; ++n)
 #pragma unroll
       for (int half = 0; half < 2; ++half) {
-        const int r = m * 16 + (lane >> 2) + half * 8;
-        const int col = n0 + warp * 16 + n * 8 + (lane & 3) * 2;
+        const int r = warp_m * 32 + m * 16 + (lane >> 2) + half * 8;
+        const int col = n0 + warp_n * (8 * Shape::n_tiles) + n * 8 + (lane & 3) * 2;
         if (a_rows[r] == nullptr || col >= ff) continue;  // ff is even: the pair is whole
         const float y0 = clamped_glu(acc[0][m][n][half * 2], acc[1][m][n][half * 2], limit);
         const float y1 = clamped_glu(acc[0][m][n][half * 2 + 1], acc[1][m][n][half * 2 + 1], limit);
-        *reinterpret_cast<__nv_bfloat162*>(act + (static_cast<int64_t>(tile) * kTileM + r) * ff + col) = __floats2bfloat162_rn(y0, y1);
+        *reinterpret_cast<__nv_bfloat162*>(act + (static_cast<int64_t>(tile) * Shape::rows + r) * ff + col) = __floats2bfloat162_rn(y0, y1);
       }
 }
 
-__global__ void __launch_bounds__(kMmaThreads)
+template <int MT>
+__global__ void __launch_bounds__(MmaShape<MT>::threads)
 moe_down_mma_kernel(const __nv_bfloat16* act, const __nv_bfloat16* __restrict__ weight, const int* place_slot, const int* tile_expert,
                     const int* num_tiles, int width, int ff, float* out) {
-  __shared__ __align__(16) __nv_bfloat16 a_smem[2][kTileM][kMmaPitch];
+  using Shape = MmaShape<MT>;
+  __shared__ __align__(16) __nv_bfloat16 a_smem[2][Shape::rows][kMmaPitch];
   __shared__ __align__(16) __nv_bfloat16 b_smem[2][1][kMmaN][kMmaPitch];
-  __shared__ const __nv_bfloat16* a_rows[kTileM];
-  __shared__ int row_slot[kTileM];
+  __shared__ const __nv_bfloat16* a_rows[Shape::rows];
+  __shared__ int row_slot[Shape::rows];
   wait_for_predecessor();
   let_successor_start();
   const int tile = blockIdx.x;
   if (tile >= *num_tiles) return;
   const int expert = tile_expert[tile];
   const int n0 = blockIdx.y * kMmaN;
-  if (threadIdx.x < kTileM) {
-    const int slot = place_slot[tile * kTileM + threadIdx.x];
+  if (threadIdx.x < Shape::rows) {
+    const int slot = place_slot[tile * Shape::rows + threadIdx.x];
     row_slot[threadIdx.x] = slot;
-    a_rows[threadIdx.x] = slot < 0 ? nullptr : act + (static_cast<int64_t>(tile) * kTileM + threadIdx.x) * ff;
+    a_rows[threadIdx.x] = slot < 0 ? nullptr : act + (static_cast<int64_t>(tile) * Shape::rows + threadIdx.x) * ff;
   }
   __syncthreads();
   const __nv_bfloat16* const b_rows[1] = {weight + (static_cast<int64_t>(expert) * width + n0) * ff};
-  float acc[1][2][2][4];
-  tile_product<1>(a_rows, b_rows, min(kMmaN, width - n0), ff, a_smem, b_smem, acc);
+  float acc[1][2][Shape::n_tiles][4];
+  tile_product<1, MT>(a_rows, b_rows, min(kMmaN, width - n0), ff, a_smem, b_smem, acc);
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int warp_m = warp / Shape::warps_n, warp_n = warp % Shape::warps_n;
 #pragma unroll
   for (int m = 0; m < 2; ++m)
 #pragma unroll
-    for (int n = 0; n < 2; ++n)
+    for (int n = 0; n < Shape::n_tiles; ++n)
 #pragma unroll
       for (int half = 0; half < 2; ++half) {
-        const int r = m * 16 + (lane >> 2) + half * 8;
-        const int col = n0 + warp * 16 + n * 8 + (lane & 3) * 2;
+        const int r = warp_m * 32 + m * 16 + (lane >> 2) + half * 8;
+        const int col = n0 + warp_n * (8 * Shape::n_tiles) + n * 8 + (lane & 3) * 2;
         if (row_slot[r] < 0 || col >= width) continue;  // width is even: the pair is whole
         *reinterpret_cast<float2*>(out + static_cast<int64_t>(row_slot[r]) * width + col) = make_float2(acc[0][m][n][half * 2], acc[0][m][n][half * 2 + 1]);
       }
@@ -482,36 +507,49 @@ B200_API int b200_moe_route(const float* z, int tokens, int experts, int groups,
   return b200_check_launch("moe_route");
 }
 
-B200_API int b200_moe_sort(const int* ids, int slots, int experts, int capacity, int* place_slot, int* tile_expert, int* num_tiles,
-                           cudaStream_t stream) {
+B200_API int b200_moe_sort(const int* ids, int slots, int experts, int capacity, int tile_rows, int* place_slot, int* tile_expert,
+                           int* num_tiles, cudaStream_t stream) {
   if (slots == 0) return 0;
   B200_REQUIRE(slots > 0 && experts > 0 && capacity >= slots, "moe_sort: bad sizes");
-  B200_REQUIRE(capacity % kTileM == 0 && capacity / kTileM >= (slots + experts * (kTileM - 1)) / kTileM,
+  B200_REQUIRE(tile_rows == kTileM || tile_rows == kTileM * kWideTiles, "moe_sort: tiles of %d or %d rows", kTileM, kTileM * kWideTiles);
+  B200_REQUIRE(capacity % tile_rows == 0 && capacity / tile_rows >= (slots + experts * (tile_rows - 1)) / tile_rows,
                "moe_sort: %d places do not hold %d slots of %d experts in whole tiles", capacity, slots, experts);
   const size_t smem = sizeof(int) * 2 * experts;
   B200_REQUIRE(smem <= 48 * 1024, "moe_sort: too many experts");
-  launch_kernel(moe_sort_kernel, dim3(1), dim3(1024), smem, stream, ids, slots, experts, capacity, place_slot, tile_expert, num_tiles);
+  launch_kernel(moe_sort_kernel, dim3(1), dim3(1024), smem, stream, ids, slots, experts, capacity, tile_rows, place_slot, tile_expert,
+                num_tiles);
   return b200_check_launch("moe_sort");
 }
 
 static bool aligned16(const void* p) { return reinterpret_cast<uintptr_t>(p) % 16 == 0; }
 
-// `use_mma`: bfloat16 on tensor cores where the sizes allow (K a multiple of 8); 0 keeps the plain kernel.
+// Whether the tensor-core form takes these sizes (bfloat16; K a multiple of 8 for both products).
+B200_API int b200_moe_mma_supported(int width, int ff) { return width % 8 == 0 && ff % 8 == 0 ? 1 : 0; }
+
+// `tile_rows`: what `moe_sort` was given. kTileM: the plain kernels, or with `use_mma` (bfloat16, sizes that
+// `moe_mma_supported` takes) the tensor-core form; four times kTileM: the tensor-core form only.
 B200_API int b200_moe_gate_up(const void* h, const void* weight, const int* place_slot, const int* tile_expert, const int* num_tiles,
-                              int max_tiles, int top, int width, int ff, float limit, void* act, int dtype, int use_mma,
+                              int max_tiles, int tile_rows, int top, int width, int ff, float limit, void* act, int dtype, int use_mma,
                               cudaStream_t stream) {
   if (max_tiles == 0) return 0;
   B200_REQUIRE(max_tiles > 0 && top > 0 && width > 0 && ff > 0 && limit > 0.f, "moe_gate_up: bad sizes");
+  const bool mma = dtype == DTYPE_BF16 && use_mma && b200_moe_mma_supported(width, ff) && aligned16(h) && aligned16(weight) && aligned16(act);
+  B200_REQUIRE(tile_rows == kTileM || (mma && tile_rows == kTileM * kWideTiles), "moe_gate_up: tiles of %d rows are not taken here", tile_rows);
   const dim3 grid(max_tiles, (ff + kTileN - 1) / kTileN);
   B200_REQUIRE(grid.y <= 65535, "moe_gate_up: too many columns");
   if (dtype == DTYPE_F32) {
     launch_kernel(moe_gate_up_kernel<float>, grid, dim3(kGemmThreads), 0, stream, static_cast<const float*>(h),
                   static_cast<const float*>(weight), place_slot, tile_expert, num_tiles, top, width, ff, limit, static_cast<float*>(act));
-  } else if (dtype == DTYPE_BF16 && use_mma && width % 8 == 0 && ff % 8 == 0 && aligned16(h) && aligned16(weight) && aligned16(act)) {
+  } else if (mma) {
     const dim3 mma_grid(max_tiles, (ff + kMmaN - 1) / kMmaN);
-    launch_kernel(moe_gate_up_mma_kernel, mma_grid, dim3(kMmaThreads), 0, stream, static_cast<const __nv_bfloat16*>(h),
-                  static_cast<const __nv_bfloat16*>(weight), place_slot, tile_expert, num_tiles, top, width, ff, limit,
-                  static_cast<__nv_bfloat16*>(act));
+    if (tile_rows == kTileM)
+      launch_kernel(moe_gate_up_mma_kernel<1>, mma_grid, dim3(MmaShape<1>::threads), 0, stream, static_cast<const __nv_bfloat16*>(h),
+                    static_cast<const __nv_bfloat16*>(weight), place_slot, tile_expert, num_tiles, top, width, ff, limit,
+                    static_cast<__nv_bfloat16*>(act));
+    else
+      launch_kernel(moe_gate_up_mma_kernel<kWideTiles>, mma_grid, dim3(MmaShape<kWideTiles>::threads), 0, stream,
+                    static_cast<const __nv_bfloat16*>(h), static_cast<const __nv_bfloat16*>(weight), place_slot, tile_expert, num_tiles, top,
+                    width, ff, limit, static_cast<__nv_bfloat16*>(act));
   } else if (dtype == DTYPE_BF16) {
     launch_kernel(moe_gate_up_kernel<__nv_bfloat16>, grid, dim3(kGemmThreads), 0, stream, static_cast<const __nv_bfloat16*>(h),
                   static_cast<const __nv_bfloat16*>(weight), place_slot, tile_expert, num_tiles, top, width, ff, limit,
@@ -523,18 +561,25 @@ B200_API int b200_moe_gate_up(const void* h, const void* weight, const int* plac
 }
 
 B200_API int b200_moe_down(const void* act, const void* weight, const int* place_slot, const int* tile_expert, const int* num_tiles,
-                           int max_tiles, int width, int ff, float* out, int dtype, int use_mma, cudaStream_t stream) {
+                           int max_tiles, int tile_rows, int width, int ff, float* out, int dtype, int use_mma, cudaStream_t stream) {
   if (max_tiles == 0) return 0;
   B200_REQUIRE(max_tiles > 0 && width > 0 && ff > 0, "moe_down: bad sizes");
+  const bool mma = dtype == DTYPE_BF16 && use_mma && b200_moe_mma_supported(width, ff) && aligned16(act) && aligned16(weight) && aligned16(out);
+  B200_REQUIRE(tile_rows == kTileM || (mma && tile_rows == kTileM * kWideTiles), "moe_down: tiles of %d rows are not taken here", tile_rows);
   const dim3 grid(max_tiles, (width + kTileN - 1) / kTileN);
   B200_REQUIRE(grid.y <= 65535, "moe_down: too many columns");
   if (dtype == DTYPE_F32) {
     launch_kernel(moe_down_kernel<float>, grid, dim3(kGemmThreads), 0, stream, static_cast<const float*>(act),
                   static_cast<const float*>(weight), place_slot, tile_expert, num_tiles, width, ff, out);
-  } else if (dtype == DTYPE_BF16 && use_mma && width % 8 == 0 && ff % 8 == 0 && aligned16(act) && aligned16(weight) && aligned16(out)) {
+  } else if (mma) {
     const dim3 mma_grid(max_tiles, (width + kMmaN - 1) / kMmaN);
-    launch_kernel(moe_down_mma_kernel, mma_grid, dim3(kMmaThreads), 0, stream, static_cast<const __nv_bfloat16*>(act),
-                  static_cast<const __nv_bfloat16*>(weight), place_slot, tile_expert, num_tiles, width, ff, out);
+    if (tile_rows == kTileM)
+      launch_kernel(moe_down_mma_kernel<1>, mma_grid, dim3(MmaShape<1>::threads), 0, stream, static_cast<const __nv_bfloat16*>(act),
+                    static_cast<const __nv_bfloat16*>(weight), place_slot, tile_expert, num_tiles, width, ff, out);
+    else
+      launch_kernel(moe_down_mma_kernel<kWideTiles>, mma_grid, dim3(MmaShape<kWideTiles>::threads), 0, stream,
+                    static_cast<const __nv_bfloat16*>(act), static_cast<const __nv_bfloat16*>(weight), place_slot, tile_expert, num_tiles,
+                    width, ff, out);
   } else if (dtype == DTYPE_BF16) {
     launch_kernel(moe_down_kernel<__nv_bfloat16>, grid, dim3(kGemmThreads), 0, stream, static_cast<const __nv_bfloat16*>(act),
                   static_cast<const __nv_bfloat16*>(weight), place_slot, tile_expert, num_tiles, width, ff, out);

@@ -995,23 +995,27 @@ def moe_experts(
     _need(h.is_contiguous() and w_gate_up.is_contiguous() and w_down.is_contiguous() and w_gate_up.dtype == h.dtype and w_down.dtype == h.dtype, "moe_experts: bad operands")
     _need(tuple(w_gate_up.shape) == (experts, 2 * ff, width) and tuple(w_down.shape) == (experts, width, ff), "moe_experts: bad weights")
     _need(out.dtype == torch.float32 and tuple(out.shape) == (slots, width) and out.is_contiguous(), "moe_experts: bad output")
+    # bfloat16 runs on tensor cores where the sizes allow (options["moe"] = "plain": the FMA kernels), and a step with
+    # many slots per expert sorts them into tiles four times as tall, so that a weight tile serves 128 rows.
+    tensor_cores = h.dtype == torch.bfloat16 and ctx.options.get("moe", "auto") != "plain" and bool(ctx.lib.lib.b200_moe_mma_supported(width, ff))
     tile = moe_tile_rows(ctx)
+    if tensor_cores and slots >= 2 * 4 * tile * experts:
+        tile *= 4
     max_tiles = (slots + experts * (tile - 1)) // tile + 1
     capacity = max_tiles * tile
     place_slot = ctx.buffer("moe_place_slot", (capacity,), torch.int32, per_token=False)
     tile_expert = ctx.buffer("moe_tile_expert", (max_tiles + 1,), torch.int32, per_token=False)
     act = ctx.buffer("moe_act", (capacity, ff), per_token=False)
     num_tiles = tile_expert[max_tiles:]
-    ctx.lib.call("b200_moe_sort", ptr(ids), c_int(slots), c_int(experts), c_int(capacity), ptr(place_slot), ptr(tile_expert), ptr(num_tiles), ctx.stream)
-    code = c_int(dtype_code(h.dtype))
-    tensor_cores = c_int(0 if ctx.options.get("moe", "auto") == "plain" else 1)  # bfloat16 only; "plain": the FMA kernels
+    ctx.lib.call("b200_moe_sort", ptr(ids), c_int(slots), c_int(experts), c_int(capacity), c_int(tile), ptr(place_slot), ptr(tile_expert), ptr(num_tiles), ctx.stream)
+    code, use = c_int(dtype_code(h.dtype)), c_int(1 if tensor_cores else 0)
     ctx.lib.call(
-        "b200_moe_gate_up", ptr(h), ptr(w_gate_up), ptr(place_slot), ptr(tile_expert), ptr(num_tiles), c_int(max_tiles), c_int(top),
-        c_int(width), c_int(ff), c_float(limit), ptr(act), code, tensor_cores, ctx.stream,
+        "b200_moe_gate_up", ptr(h), ptr(w_gate_up), ptr(place_slot), ptr(tile_expert), ptr(num_tiles), c_int(max_tiles), c_int(tile), c_int(top),
+        c_int(width), c_int(ff), c_float(limit), ptr(act), code, use, ctx.stream,
     )
     ctx.lib.call(
-        "b200_moe_down", ptr(act), ptr(w_down), ptr(place_slot), ptr(tile_expert), ptr(num_tiles), c_int(max_tiles), c_int(width), c_int(ff),
-        ptr(out), code, tensor_cores, ctx.stream,
+        "b200_moe_down", ptr(act), ptr(w_down), ptr(place_slot), ptr(tile_expert), ptr(num_tiles), c_int(max_tiles), c_int(tile), c_int(width),
+        c_int(ff), ptr(out), code, use, ctx.stream,
     )
     return out
 

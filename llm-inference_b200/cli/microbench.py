@@ -307,6 +307,53 @@ def bench_delta_recurrence(args) -> dict:
             "us_per_token": us / tokens, "GBps": moved / us / 1e3, "TFLOPs": 7.0 * total * heads * dk * dv / us / 1e6}
 
 
+def bench_wkv_recurrence(args) -> dict:
+    """The recurrence of the mixer with a decay per channel and a bonus for the current token
+    (parts/wkv.py) over ``--batch`` requests of ``--tokens`` tokens each: ``--q-heads`` heads with states of
+    ``--head-dim`` x ``--head-dim``. Flops: per token and head two products over the state (read-out; decay
+    and update)."""
+    from ..parts import ops
+
+    heads, dim, batch, tokens = args.q_heads, args.head_dim, args.batch, args.tokens
+    runs, starts = [tokens] * batch, [0] * batch
+    ctx = make_ctx([p for r in runs for p in range(r)], [i for i, r in enumerate(runs) for _ in range(r)], starts, runs)
+    ctx.seq_slot = torch.arange(batch, dtype=torch.int32, device="cuda")
+    total = batch * tokens
+    r, k, v = (torch.randn(total, heads * dim, device="cuda") for _ in range(3))
+    bonus = torch.randn(total, heads, device="cuda")
+    decay = torch.rand(total, heads * dim, device="cuda") * 0.2 + 0.8
+    state = torch.zeros(batch, heads, dim, dim, device="cuda")
+    out = torch.empty(total, heads * dim, device="cuda")
+    us = time_launches(lambda: ops.wkv_recurrence(ctx, r, k, v, bonus, decay, state, out, heads, dim, dim), args.iters)
+    moved = 4.0 * (total * (5 * heads * dim + heads) + 2 * batch * heads * dim * dim)
+    return {"kernel": "wkv_recurrence", "batch": batch, "tokens": tokens, "heads": heads, "dim": dim, "us": us,
+            "us_per_token": us / tokens, "GBps": moved / us / 1e3, "TFLOPs": 5.0 * total * heads * dim * dim / us / 1e6}
+
+
+def bench_moe_experts(args) -> dict:
+    """The routed experts' two products (parts/feed_forward.py, ``routed_experts``) for ``--tokens`` tokens of width
+    ``--k``: ``--experts`` experts of inner width ``--n``, ``--top`` per token chosen at random; bfloat16 on tensor
+    cores unless ``--plain``. Flops: 6 x slots x inner x width. Bytes: every chosen expert's weights once plus the
+    slots' rows in and out."""
+    from ..parts import ops
+
+    tokens, width, ff, experts, top = args.tokens, args.k, args.n, args.experts, args.top
+    ctx = make_ctx(list(range(tokens)), [0] * tokens, options={"moe": "plain"} if args.plain else {})
+    ctx.dtype = torch.bfloat16
+    h = torch.randn(tokens, width, device="cuda", dtype=torch.bfloat16)
+    w_gate_up = torch.randn(experts, 2 * ff, width, device="cuda", dtype=torch.bfloat16) * width**-0.5
+    w_down = torch.randn(experts, width, ff, device="cuda", dtype=torch.bfloat16) * ff**-0.5
+    ids = torch.stack([torch.randperm(experts, device="cuda")[:top] for _ in range(tokens)]).to(torch.int32).contiguous()
+    out = torch.empty(tokens * top, width, device="cuda")
+    ctx.buffer = lambda name, shape, dtype=None, per_token=True: ctx.workspace.get(name, shape, dtype or torch.bfloat16, per_token=per_token)
+    us = time_launches(lambda: ops.moe_experts(ctx, h, ids, w_gate_up, w_down, 7.0, out), args.iters)
+    used = int(torch.unique(ids).numel())
+    slots = tokens * top
+    moved = 2.0 * used * 3 * ff * width + 2.0 * slots * (width + 2 * ff) + 4.0 * slots * width
+    return {"kernel": "moe_experts (sort + gate/up + down)", "tokens": tokens, "width": width, "inner": ff, "experts": experts, "top": top,
+            "experts_used": used, "us": us, "TFLOPs": 6.0 * slots * ff * width / us / 1e6, "GBps": moved / us / 1e3}
+
+
 def bench_resident(args) -> dict:
     """One decode step as the resident kernel at a named shape: time per step, and for each kind of
     phase how long the slowest block takes to ask for its operand, to finish, and how long block 0
@@ -421,7 +468,10 @@ def bench_timeline(args) -> dict:
 def main(argv=None) -> int:
     parser = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
     parser.add_argument("kernel", choices=["gemm", "decode_attention", "prefill_attention", "resident", "timeline",
-                                           "latent_decode_attention", "latent_prefill_attention", "delta_recurrence"])
+                                           "latent_decode_attention", "latent_prefill_attention", "delta_recurrence", "wkv_recurrence",
+                                           "moe_experts"])
+    parser.add_argument("--experts", type=int, default=32, help="moe_experts: number of experts")
+    parser.add_argument("--top", type=int, default=4, help="moe_experts: experts per token")
     parser.add_argument("--rank", type=int, default=512, help="latent attention: size of the cached latent")
     parser.add_argument("--rot-dim", type=int, default=64, help="latent attention: size of the shared rotated key part")
     parser.add_argument("--vdim", type=int, default=128, help="delta_recurrence: value size per head")
@@ -466,6 +516,10 @@ def main(argv=None) -> int:
         result = bench_latent_attention(args, args.kernel == "latent_decode_attention")
     elif args.kernel == "delta_recurrence":
         result = bench_delta_recurrence(args)
+    elif args.kernel == "wkv_recurrence":
+        result = bench_wkv_recurrence(args)
+    elif args.kernel == "moe_experts":
+        result = bench_moe_experts(args)
     else:
         result = bench_attention(args, args.kernel == "decode_attention")
     print(json.dumps(result))

@@ -293,13 +293,13 @@ def gunedra_shape(width: int) -> dict:
 
 def tunadra_shape(width: int) -> dict:
     """Layer sizes in the proportions of a real model of this design: attention heads of 128 sharing
-    key/value heads as the Qwen2 shape does, recurrent heads of 64 x 64, three streams, and a routed
+    key/value heads as the Qwen2 shape does, recurrent heads of 64 x 64, four streams, and a routed
     feed-forward of 32 experts (four groups, two kept, four experts per token) plus a shared expert, sized
     so that a token passes through as many feed-forward weights as in the dense shape of this width."""
     heads, ff = DESIGN_SIZES[width]
     mlp = {
         "kind": "moe", "expert": {"ff": ff // 8, "limit": 7.0}, "shared": {"ff": ff // 2, "limit": 7.0},
-        "router": {"experts": 32, "top": 4, "scale": 2.5, "groups": {"count": 4, "keep": 2}},
+        "router": {"experts": 32, "top": 4, "scale": 2.0, "groups": {"count": 4, "keep": 2}},
     }
     attention = {
         "type": "attention", "mlp": mlp,
@@ -307,7 +307,7 @@ def tunadra_shape(width: int) -> dict:
     }
     recurrent = {"type": "wkv", "mlp": mlp, "mixer": {"heads": width // 64, "dim": 64, "decay_rank": 64}}
     return {
-        "architecture": "Tunadra", "vocab": DESIGN_VOCAB, "width": width, "streams": 3, "logit_softcap": 30.0,
+        "architecture": "Tunadra", "vocab": DESIGN_VOCAB, "width": width, "streams": 4, "logit_softcap": 50.0,
         "embedding": {"scale": width ** 0.5}, "norm": {"eps": 1e-5}, "layers": [attention, attention, recurrent, attention][:DESIGN_LAYERS],
     }
 

@@ -24,7 +24,23 @@ def _qwen2(layers, hidden, heads, kv_heads, inter, vocab, tied, max_pos=32768, *
     return config
 
 
+def _tunadra(width, vocab, blocks, heads, kv_heads, experts, top, ff):
+    """``blocks`` pairs of (attention layer, recurrent layer); the attention layers blend their values."""
+    mlp = {
+        "kind": "moe", "expert": {"ff": ff, "limit": 7.0}, "shared": {"ff": 2 * ff, "limit": 7.0},
+        "router": {"experts": experts, "top": top, "scale": 2.0, "groups": {"count": 4, "keep": 2}},
+    }
+    attention = {"type": "attention", "mlp": mlp,
+                 "mixer": {"heads": heads, "kv_heads": kv_heads, "dim": 64, "vdim": 64, "scale": 0.125, "v_mix": True}}
+    recurrent = {"type": "wkv", "mlp": mlp, "mixer": {"heads": width // 64, "dim": 64, "decay_rank": 32}}
+    return {
+        "architecture": "Tunadra", "vocab": vocab, "width": width, "streams": 2, "logit_softcap": 50.0,
+        "embedding": {"scale": float(width) ** 0.5}, "norm": {"eps": 1e-5}, "layers": [attention, recurrent] * blocks,
+    }
+
+
 PRESETS = {
+    "tunadra-small": _tunadra(512, 8192, 3, 8, 2, 16, 2, 256),
     "tiny-a": _qwen2(2, 64, 4, 2, 176, 256, True, 128, rope_theta=10000.0),
     "tiny-b": _qwen2(3, 96, 3, 1, 272, 311, False, 256, rms_norm_eps=1e-5, use_sliding_window=True,
                      sliding_window=24, max_window_layers=1),

@@ -255,15 +255,18 @@ moe_down_kernel(const T* act, const T* __restrict__ weight, const int* place_slo
 
 // The same two products on tensor cores (bfloat16 operands, 32-bit sums): a block takes one tile of
 // 32 * MT sorted places and kMmaN output columns of each of its MATS matrices (2: gate and up with the
-// activation as epilogue; 1: down) and walks K in steps of kMmaK through two cp.async stages;
+// activation as epilogue; 1: down) and walks K in steps of kMmaK through a ring of kMmaStages cp.async stages
+// in dynamic shared memory (one block barrier a step: a stage is refilled right after the barrier that
+// follows its last use);
 // fragments by ldmatrix, `mma.sync` m16n8k16. MT = 1 (steps with few tokens per expert: four warps, 16
 // columns each) or 4 (prompt portions: eight warps as 4 x 2, each 32 rows x 32 columns, so that a
 // weight tile fetched from L2 serves 128 rows). A row's sums depend on the row, the weights and K only
 // (a fixed order of k steps), not on the tile's other rows or on MT. Rows of A start at `a_rows[r]`
 // (null: zeros); K must be a multiple of 8 (16-byte copies).
 constexpr int kMmaN = 64;
-constexpr int kMmaK = 32;
-constexpr int kMmaPitch = kMmaK + 8;  // 80 bytes a row: ldmatrix reads without bank conflicts
+constexpr int kMmaK = 64;
+constexpr int kMmaPitch = kMmaK + 8;  // 144 bytes a row: ldmatrix reads without bank conflicts
+constexpr int kMmaStages = 3;
 constexpr int kWideTiles = 4;         // MT of the prompt form
 
 template <int MT>
@@ -272,6 +275,7 @@ struct MmaShape {
   static constexpr int threads = MT == 1 ? 128 : 256;
   static constexpr int warps_n = MT == 1 ? 4 : 2;
   static constexpr int n_tiles = kMmaN / warps_n / 8;  // n8 tiles a warp: 2 or 4
+  static constexpr size_t smem(int mats) { return sizeof(__nv_bfloat16) * kMmaStages * (rows + mats * kMmaN) * kMmaPitch; }
 };
 
 __device__ __forceinline__ void copy16(void* smem, const void* gmem, bool valid) {
@@ -308,9 +312,9 @@ __device__ __forceinline__ void tile_product(const __nv_bfloat16* const* a_rows,
         for (int i = 0; i < 4; ++i) acc[mat][m][n][i] = 0.f;
   auto fetch = [&](int stage, int k0) {
 #pragma unroll
-    for (int i = 0; i < Shape::rows * 4 / Shape::threads; ++i) {
+    for (int i = 0; i < Shape::rows * (kMmaK / 8) / Shape::threads; ++i) {
       const int chunk = tid + i * Shape::threads;
-      const int r = chunk >> 2, c = (chunk & 3) * 8;
+      const int r = chunk / (kMmaK / 8), c = (chunk % (kMmaK / 8)) * 8;
       const __nv_bfloat16* src = a_rows[r];
       const bool in = src != nullptr && k0 + c < K;
       copy16(&a_smem[stage][r][c], in ? src + k0 + c : b_rows[0], in);
@@ -318,22 +322,25 @@ __device__ __forceinline__ void tile_product(const __nv_bfloat16* const* a_rows,
 #pragma unroll
     for (int mat = 0; mat < MATS; ++mat)
 #pragma unroll
-      for (int i = 0; i < kMmaN * 4 / Shape::threads; ++i) {
+      for (int i = 0; i < kMmaN * (kMmaK / 8) / Shape::threads; ++i) {
         const int chunk = tid + i * Shape::threads;
-        const int r = chunk >> 2, c = (chunk & 3) * 8;
+        const int r = chunk / (kMmaK / 8), c = (chunk % (kMmaK / 8)) * 8;
         const bool in = r < n_valid && k0 + c < K;
         copy16(&b_smem[stage][mat][r][c], in ? b_rows[mat] + static_cast<int64_t>(r) * K + k0 + c : b_rows[0], in);
       }
   };
   const int steps = (K + kMmaK - 1) / kMmaK;
-  fetch(0, 0);
-  asm volatile("cp.async.commit_group;" ::: "memory");
-  for (int step = 0; step < steps; ++step) {
-    const int stage = step & 1;
-    if (step + 1 < steps) fetch(stage ^ 1, (step + 1) * kMmaK);
+#pragma unroll
+  for (int ahead = 0; ahead < kMmaStages - 1; ++ahead) {
+    if (ahead < steps) fetch(ahead, ahead * kMmaK);
     asm volatile("cp.async.commit_group;" ::: "memory");
-    asm volatile("cp.async.wait_group 1;" ::: "memory");
-    __syncthreads();
+  }
+  for (int step = 0; step < steps; ++step) {
+    const int stage = step % kMmaStages;
+    asm volatile("cp.async.wait_group %0;" ::"n"(kMmaStages - 2) : "memory");
+    __syncthreads();  // this step's stage has landed for everyone, and everyone is done with the stage refilled next
+    if (step + kMmaStages - 1 < steps) fetch((step + kMmaStages - 1) % kMmaStages, (step + kMmaStages - 1) * kMmaK);
+    asm volatile("cp.async.commit_group;" ::: "memory");
 #pragma unroll
     for (int kk = 0; kk < kMmaK; kk += 16) {
       uint32_t a[2][4];
@@ -353,7 +360,6 @@ __device__ __forceinline__ void tile_product(const __nv_bfloat16* const* a_rows,
           }
         }
     }
-    __syncthreads();
   }
   asm volatile("cp.async.wait_group 0;" ::: "memory");
 }
@@ -363,8 +369,9 @@ __global__ void __launch_bounds__(MmaShape<MT>::threads)
 moe_gate_up_mma_kernel(const __nv_bfloat16* h, const __nv_bfloat16* __restrict__ weight, const int* place_slot, const int* tile_expert,
                        const int* num_tiles, int top, int width, int ff, float limit, __nv_bfloat16* act) {
   using Shape = MmaShape<MT>;
-  __shared__ __align__(16) __nv_bfloat16 a_smem[2][Shape::rows][kMmaPitch];
-  __shared__ __align__(16) __nv_bfloat16 b_smem[2][2][kMmaN][kMmaPitch];
+  extern __shared__ __align__(16) unsigned char mma_smem[];
+  auto a_smem = reinterpret_cast<__nv_bfloat16(*)[Shape::rows][kMmaPitch]>(mma_smem);
+  auto b_smem = reinterpret_cast<__nv_bfloat16(*)[2][kMmaN][kMmaPitch]>(mma_smem + sizeof(__nv_bfloat16) * kMmaStages * Shape::rows * kMmaPitch);
   __shared__ const __nv_bfloat16* a_rows[Shape::rows];
   wait_for_predecessor();
   let_successor_start();
@@ -403,8 +410,9 @@ __global__ void __launch_bounds__(MmaShape<MT>::threads)
 moe_down_mma_kernel(const __nv_bfloat16* act, const __nv_bfloat16* __restrict__ weight, const int* place_slot, const int* tile_expert,
                     const int* num_tiles, int width, int ff, float* out) {
   using Shape = MmaShape<MT>;
-  __shared__ __align__(16) __nv_bfloat16 a_smem[2][Shape::rows][kMmaPitch];
-  __shared__ __align__(16) __nv_bfloat16 b_smem[2][1][kMmaN][kMmaPitch];
+  extern __shared__ __align__(16) unsigned char mma_smem[];
+  auto a_smem = reinterpret_cast<__nv_bfloat16(*)[Shape::rows][kMmaPitch]>(mma_smem);
+  auto b_smem = reinterpret_cast<__nv_bfloat16(*)[1][kMmaN][kMmaPitch]>(mma_smem + sizeof(__nv_bfloat16) * kMmaStages * Shape::rows * kMmaPitch);
   __shared__ const __nv_bfloat16* a_rows[Shape::rows];
   __shared__ int row_slot[Shape::rows];
   wait_for_predecessor();
@@ -542,14 +550,13 @@ B200_API int b200_moe_gate_up(const void* h, const void* weight, const int* plac
                   static_cast<const float*>(weight), place_slot, tile_expert, num_tiles, top, width, ff, limit, static_cast<float*>(act));
   } else if (mma) {
     const dim3 mma_grid(max_tiles, (ff + kMmaN - 1) / kMmaN);
-    if (tile_rows == kTileM)
-      launch_kernel(moe_gate_up_mma_kernel<1>, mma_grid, dim3(MmaShape<1>::threads), 0, stream, static_cast<const __nv_bfloat16*>(h),
-                    static_cast<const __nv_bfloat16*>(weight), place_slot, tile_expert, num_tiles, top, width, ff, limit,
-                    static_cast<__nv_bfloat16*>(act));
-    else
-      launch_kernel(moe_gate_up_mma_kernel<kWideTiles>, mma_grid, dim3(MmaShape<kWideTiles>::threads), 0, stream,
-                    static_cast<const __nv_bfloat16*>(h), static_cast<const __nv_bfloat16*>(weight), place_slot, tile_expert, num_tiles, top,
-                    width, ff, limit, static_cast<__nv_bfloat16*>(act));
+    auto launch = [&](auto kernel, int threads, size_t smem) {
+      if (smem > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+      launch_kernel(kernel, mma_grid, dim3(threads), smem, stream, static_cast<const __nv_bfloat16*>(h), static_cast<const __nv_bfloat16*>(weight),
+                    place_slot, tile_expert, num_tiles, top, width, ff, limit, static_cast<__nv_bfloat16*>(act));
+    };
+    if (tile_rows == kTileM) launch(moe_gate_up_mma_kernel<1>, MmaShape<1>::threads, MmaShape<1>::smem(2));
+    else launch(moe_gate_up_mma_kernel<kWideTiles>, MmaShape<kWideTiles>::threads, MmaShape<kWideTiles>::smem(2));
   } else if (dtype == DTYPE_BF16) {
     launch_kernel(moe_gate_up_kernel<__nv_bfloat16>, grid, dim3(kGemmThreads), 0, stream, static_cast<const __nv_bfloat16*>(h),
                   static_cast<const __nv_bfloat16*>(weight), place_slot, tile_expert, num_tiles, top, width, ff, limit,
@@ -573,13 +580,13 @@ B200_API int b200_moe_down(const void* act, const void* weight, const int* place
                   static_cast<const float*>(weight), place_slot, tile_expert, num_tiles, width, ff, out);
   } else if (mma) {
     const dim3 mma_grid(max_tiles, (width + kMmaN - 1) / kMmaN);
-    if (tile_rows == kTileM)
-      launch_kernel(moe_down_mma_kernel<1>, mma_grid, dim3(MmaShape<1>::threads), 0, stream, static_cast<const __nv_bfloat16*>(act),
-                    static_cast<const __nv_bfloat16*>(weight), place_slot, tile_expert, num_tiles, width, ff, out);
-    else
-      launch_kernel(moe_down_mma_kernel<kWideTiles>, mma_grid, dim3(MmaShape<kWideTiles>::threads), 0, stream,
-                    static_cast<const __nv_bfloat16*>(act), static_cast<const __nv_bfloat16*>(weight), place_slot, tile_expert, num_tiles,
-                    width, ff, out);
+    auto launch = [&](auto kernel, int threads, size_t smem) {
+      if (smem > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+      launch_kernel(kernel, mma_grid, dim3(threads), smem, stream, static_cast<const __nv_bfloat16*>(act), static_cast<const __nv_bfloat16*>(weight),
+                    place_slot, tile_expert, num_tiles, width, ff, out);
+    };
+    if (tile_rows == kTileM) launch(moe_down_mma_kernel<1>, MmaShape<1>::threads, MmaShape<1>::smem(1));
+    else launch(moe_down_mma_kernel<kWideTiles>, MmaShape<kWideTiles>::threads, MmaShape<kWideTiles>::smem(1));
   } else if (dtype == DTYPE_BF16) {
     launch_kernel(moe_down_kernel<__nv_bfloat16>, grid, dim3(kGemmThreads), 0, stream, static_cast<const __nv_bfloat16*>(act),
                   static_cast<const __nv_bfloat16*>(weight), place_slot, tile_expert, num_tiles, width, ff, out);

@@ -24,3 +24,19 @@ __device__ __forceinline__ void clear_page_tail(T* tile, int first_row, int page
     for (int i = threadIdx.x; i < count; i += blockDim.x) elems[i] = from_f32<T>(0.f);
   }
 }
+
+// Clears rows `first_row .. page_size` of one (page, kv head) tile, which are contiguous, by one warp.
+template <typename T>
+__device__ __forceinline__ void clear_page_tail_by_warp(T* tile, int first_row, int page_size, int row_dim, int lane) {
+  if (first_row >= page_size) return;
+  const int64_t begin = static_cast<int64_t>(first_row) * row_dim * sizeof(T);
+  const int64_t end = static_cast<int64_t>(page_size) * row_dim * sizeof(T);
+  unsigned char* base = reinterpret_cast<unsigned char*>(tile);
+  if ((static_cast<int64_t>(row_dim) * sizeof(T)) % 16 == 0 && reinterpret_cast<uintptr_t>(base) % 16 == 0) {
+    for (int64_t at = begin + lane * 16; at < end; at += 32 * 16) *reinterpret_cast<uint4*>(base + at) = make_uint4(0u, 0u, 0u, 0u);
+  } else {
+    T* elems = tile + static_cast<int64_t>(first_row) * row_dim;
+    const int count = (page_size - first_row) * row_dim;
+    for (int i = lane; i < count; i += 32) elems[i] = from_f32<T>(0.f);
+  }
+}

@@ -106,7 +106,7 @@ def test_soft_cap_of_logits():
     assert np.abs(got).max() < 30.0 and np.abs(logits).max() > 60.0
 
 
-@pytest.mark.parametrize("experts,groups,keep,top", [(16, 4, 3, 4), (8, 4, 2, 2), (6, 2, 1, 3), (5, 5, 3, 1), (12, 1, 1, 5), (64, 8, 4, 8), (3, 3, 3, 3), (96, 1, 1, 40)])
+@pytest.mark.parametrize("experts,groups,keep,top", [(20, 5, 3, 4), (8, 4, 2, 2), (6, 2, 1, 3), (5, 5, 3, 1), (12, 1, 1, 5), (64, 8, 4, 8), (3, 3, 3, 3), (96, 1, 1, 40)])
 def test_router_choices_and_weights(experts, groups, keep, top):
     """Random logits, plus rows made so that the largest score of all sits in a group that loses (its
     neighbours are small) while a group of two middling scores wins."""
@@ -581,3 +581,22 @@ def test_greedy_generation_through_the_engine(model_case):
             assert row.max() - row[token] <= 0.1 * row.std()
             break
         tokens.append(token)
+
+
+def test_command_line_tools_take_the_design(tmp_path):
+    """A seeded folder from the named shape, its inspection, and greedy generation from the folder and from
+    the shape itself (weights drawn on the device)."""
+    run = lambda *args: subprocess.run([sys.executable, "-m", *args], capture_output=True, text=True, timeout=600)
+    folder = tmp_path / "model"
+    made = run("llm_inference_b200.cli.random_model", "--preset", "tunadra-small", "--seed", "3", "--out", str(folder))
+    assert made.returncode == 0, made.stderr[-2000:]
+    seen = run("llm_inference_b200.cli.inspect_model", str(folder))
+    assert seen.returncode == 0 and "architecture: Tunadra" in seen.stdout and "l1.mix.w0" in seen.stdout, seen.stderr[-2000:]
+    ask = ["--prompt-ids", "5,17,3,900,41", "--max-new-tokens", "6", "--max-model-length", "256", "--kv-cache-mib", "64"]
+    from_folder = run("llm_inference_b200.cli.generate", "--model", str(folder), *ask)
+    from_shape = run("llm_inference_b200.cli.generate", "--random", "tunadra-small", "--weights-seed", "3", *ask)
+    assert from_folder.returncode == 0, from_folder.stderr[-2000:]
+    assert from_shape.returncode == 0, from_shape.stderr[-2000:]
+    for result in (from_folder, from_shape):
+        line = json.loads(result.stdout.strip().splitlines()[-1])
+        assert line["prompt_tokens"] == 5 and len(line["tokens"]) == 6 and all(0 <= t < 8192 for t in line["tokens"])

@@ -69,7 +69,7 @@ BETA = config_of(
 GAMMA = config_of(
     64, 113,
     [
-        with_mlp(attention_layer(heads=3, kv_heads=1, dim=64, vdim=64, scale=0.4, v_mix=True), moe(experts=16, top=4, ff=32, groups=(4, 3), shared=(64, 2.5))),
+        with_mlp(attention_layer(heads=3, kv_heads=1, dim=64, vdim=64, scale=0.4, v_mix=True), moe(experts=12, top=3, ff=32, groups=(3, 2), shared=(64, 2.5))),
         with_mlp(wkv_layer(heads=2, dim=32, decay_rank=8), moe(experts=8, top=3, ff=48, groups=None)),
         with_mlp(attention_layer(heads=3, kv_heads=1, dim=64, vdim=64, scale=0.5, v_mix=True), moe(experts=2, top=1, ff=16, groups=(2, 2))),
     ],

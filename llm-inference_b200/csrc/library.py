@@ -100,6 +100,8 @@ _SIGNATURES: dict[str, list] = {
     "b200_moe_sort": [c_void_p, c_int, c_int, c_int, c_int] + [c_void_p] * 4,
     "b200_moe_gate_up": [c_void_p] * 5 + [c_int] * 5 + [c_float, c_void_p, c_int, c_int, c_void_p],
     "b200_moe_down": [c_void_p] * 5 + [c_int] * 4 + [c_void_p, c_int, c_int, c_void_p],
+    "b200_moe_gather_rows": [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p],
+    "b200_moe_product_tcgen05": [c_void_p] * 5 + [c_int] * 7 + [c_float, c_void_p, c_int, c_void_p, c_void_p],
     "b200_moe_combine": [c_void_p] * 3 + [c_int] * 3 + [c_void_p, c_int, c_void_p],
     "b200_clamped_glu": [c_void_p, c_int, c_int, c_float, c_void_p, c_int, c_void_p],
 }
@@ -138,6 +140,8 @@ class KernelLibrary:
         self.lib.b200_moe_tile_rows.restype = c_int
         self.lib.b200_moe_mma_supported.argtypes = [c_int, c_int]
         self.lib.b200_moe_mma_supported.restype = c_int
+        self.lib.b200_moe_tcgen05_supported.argtypes = [c_int, c_int]
+        self.lib.b200_moe_tcgen05_supported.restype = c_int
         self.lib.b200_skinny_gemm_fold_parts.argtypes = [c_int, c_int]
         self.lib.b200_skinny_gemm_fold_parts.restype = c_int
         self.lib.b200_stream_gemm_fold_parts.argtypes = [c_int, c_int, c_int]

@@ -43,7 +43,7 @@ def tunadra_recipe(config: TunadraConfig) -> ModelRecipe:
                 dict(
                     prefix=prefix + "mix.", hidden_size=hidden, heads=sizes["heads"], kv_heads=sizes["kv_heads"], dim=sizes["dim"],
                     vdim=sizes["vdim"], scale=sizes["scale"], eps=eps, qk_norm=True, gate=True, values=values,
-                    has_blend_tensor=bool(sizes.get("v_mix")),
+                    has_blend_tensor=True,  # a checkpoint may carry the factor for a layer that does not blend: it is read past
                 ),
             )
         mlp = layer.get("mlp")

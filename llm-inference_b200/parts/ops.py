@@ -985,8 +985,9 @@ def moe_experts(
     ctx: StepContext, h: torch.Tensor, ids: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, limit: float, out: torch.Tensor
 ) -> torch.Tensor:
     """``out[t * top + j] = expert ids[t, j] applied to h[t]`` (float32, not yet weighted). ``w_gate_up`` is
-    ``[experts, 2 * ff, width]`` (gate rows, then up rows), ``w_down`` ``[experts, width, ff]``. Three launches:
-    the slots are sorted by expert into runs of whole tiles, then the two products walk the tiles."""
+    ``[experts, 2 * ff, width]`` (gate rows, then up rows), ``w_down`` ``[experts, width, ff]``. The slots are sorted by
+    expert into runs of whole tiles, then the two products walk the tiles (tall tiles on tcgen05 read rows that a
+    gather pass has put into sorted order)."""
     tokens, width = h.shape
     top = ids.shape[1]
     experts, twice, _ = w_gate_up.shape
@@ -995,11 +996,14 @@ def moe_experts(
     _need(h.is_contiguous() and w_gate_up.is_contiguous() and w_down.is_contiguous() and w_gate_up.dtype == h.dtype and w_down.dtype == h.dtype, "moe_experts: bad operands")
     _need(tuple(w_gate_up.shape) == (experts, 2 * ff, width) and tuple(w_down.shape) == (experts, width, ff), "moe_experts: bad weights")
     _need(out.dtype == torch.float32 and tuple(out.shape) == (slots, width) and out.is_contiguous(), "moe_experts: bad output")
-    # bfloat16 runs on tensor cores where the sizes allow (options["moe"] = "plain": the FMA kernels), and a step with
-    # many slots per expert sorts them into tiles four times as tall, so that a weight tile serves 128 rows.
-    tensor_cores = h.dtype == torch.bfloat16 and ctx.options.get("moe", "auto") != "plain" and bool(ctx.lib.lib.b200_moe_mma_supported(width, ff))
+    # bfloat16 runs on tensor cores where the sizes allow, and a step with many slots per expert sorts them into tiles
+    # four times as tall (128 places), which the tcgen05 form takes; short steps keep tiles of 32 and mma.sync.
+    # options["moe"]: "auto", "mma" (mma.sync for tall tiles too) or "plain" (the FMA kernels).
+    choice = ctx.options.get("moe", "auto")
+    tensor_cores = h.dtype == torch.bfloat16 and choice != "plain" and bool(ctx.lib.lib.b200_moe_mma_supported(width, ff))
     tile = moe_tile_rows(ctx)
-    if tensor_cores and slots >= 2 * 4 * tile * experts:
+    tall = tensor_cores and slots >= 2 * 4 * tile * experts
+    if tall:
         tile *= 4
     max_tiles = (slots + experts * (tile - 1)) // tile + 1
     capacity = max_tiles * tile
@@ -1008,6 +1012,19 @@ def moe_experts(
     act = ctx.buffer("moe_act", (capacity, ff), per_token=False)
     num_tiles = tile_expert[max_tiles:]
     ctx.lib.call("b200_moe_sort", ptr(ids), c_int(slots), c_int(experts), c_int(capacity), c_int(tile), ptr(place_slot), ptr(tile_expert), ptr(num_tiles), ctx.stream)
+    if tall and choice == "auto" and bool(ctx.lib.lib.b200_moe_tcgen05_supported(width, ff)):
+        sorted_rows = ctx.buffer("moe_sorted_rows", (capacity, width), per_token=False)
+        ctx.lib.call("b200_moe_gather_rows", ptr(h), ptr(place_slot), c_int(capacity), c_int(top), c_int(width), ptr(sorted_rows), ctx.stream)
+        stages = c_int(int(ctx.options.get("moe_stages", 0)))
+        ctx.lib.call(
+            "b200_moe_product_tcgen05", ptr(w_gate_up), ptr(sorted_rows), ptr(place_slot), ptr(tile_expert), ptr(num_tiles), c_int(max_tiles),
+            c_int(experts), c_int(2 * ff), c_int(ff), c_int(ff), c_int(width), c_int(2), c_float(limit), ptr(act), stages, ptr(ctx.err), ctx.stream,
+        )
+        ctx.lib.call(
+            "b200_moe_product_tcgen05", ptr(w_down), ptr(act), ptr(place_slot), ptr(tile_expert), ptr(num_tiles), c_int(max_tiles),
+            c_int(experts), c_int(width), c_int(0), c_int(width), c_int(ff), c_int(1), c_float(limit), ptr(out), stages, ptr(ctx.err), ctx.stream,
+        )
+        return out
     code, use = c_int(dtype_code(h.dtype)), c_int(1 if tensor_cores else 0)
     ctx.lib.call(
         "b200_moe_gate_up", ptr(h), ptr(w_gate_up), ptr(place_slot), ptr(tile_expert), ptr(num_tiles), c_int(max_tiles), c_int(tile), c_int(top),

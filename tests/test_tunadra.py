@@ -168,32 +168,41 @@ def test_routed_experts_alone_and_a_token_alone_equals_the_token_in_a_batch(name
         assert torch.equal(alone, got[rows])
 
 
-def test_routed_experts_on_tall_tiles_equal_the_short_ones_bit_for_bit():
-    """bfloat16, 1,100 tokens over four experts: enough slots per expert that the step sorts them into
-    tiles of 128 places for the tensor-core products. Rows fed alone (tiles of 32) give the same bits,
-    and the FMA kernels the same numbers within rounding."""
+@pytest.mark.parametrize("hidden,ff,experts", [(64, 72, 4), (200, 136, 3), (48, 8, 2)])
+def test_routed_experts_on_tall_tiles(hidden, ff, experts):
+    """bfloat16, 1,100 tokens over a few experts: enough slots per expert that the step sorts them into
+    tiles of 128 places, which run on tcgen05 (rows gathered into sorted order, K and output widths that
+    are no multiples of the tile sizes). The plain implementation, the FMA kernels and rows fed alone
+    (tiles of 32, mma.sync) agree within rounding; with mma.sync for the tall tiles too, rows fed alone
+    give the same bits."""
     from llm_inference_b200.parts import PartSpec, build_part
 
-    hidden, tokens = 64, 1100
-    mlp = moe(experts=4, top=2, ff=72, groups=None, shared=(24, 2.0))
+    tokens = 1100
+    mlp = moe(experts=experts, top=2, ff=ff, groups=None, shared=(24, 2.0))
     config = dict(ALPHA, width=hidden, layers=[dict(wkv_layer(), mlp=mlp)])
     weights = {k: v for k, v in draw_weights(config, 13).items() if k.startswith("l0.mlp.")}
     part = build_part("feed_forward", PartSpec("routed_experts", dict(
-        prefix="l0.mlp.", hidden_size=hidden, experts=4, top=2, intermediate_size=72, limit=2.0, route_scale=1.5, shared_size=24, shared_limit=2.0)))
+        prefix="l0.mlp.", hidden_size=hidden, experts=experts, top=2, intermediate_size=ff, limit=2.0, route_scale=1.5, shared_size=24, shared_limit=2.0)))
     part.load(weights, torch.bfloat16, torch.device("cuda:0"))
     h = rounded(np.random.default_rng(1).normal(0, 1, (tokens, hidden)), torch.bfloat16)
     want = plain.moe(h.double().numpy(), as_float64(weights), "l0.mlp.", mlp)
-    _, _, ctx = context_for({}, torch.bfloat16, [1])
+    runner, _, ctx = context_for({}, torch.bfloat16, [1])
     ctx.num_tokens = tokens
     got = part.forward(ctx, h.cuda()).clone()
+    runner.check()
     scale = np.abs(want).max()
     np.testing.assert_allclose(got.double().cpu().numpy() / scale, want / scale, atol=2e-2, rtol=0)
     ctx.options = dict(ctx.options, moe="plain")
     simple = part.forward(ctx, h.cuda()).clone()
     np.testing.assert_allclose(simple.double().cpu().numpy() / scale, got.double().cpu().numpy() / scale, atol=1e-2, rtol=0)
+    ctx.options = dict(ctx.options, moe="mma")
+    legacy = part.forward(ctx, h.cuda()).clone()
+    np.testing.assert_allclose(legacy.double().cpu().numpy() / scale, got.double().cpu().numpy() / scale, atol=1e-2, rtol=0)
     for rows in ([7], [1099, 3, 640]):
         _, _, small = context_for({}, torch.bfloat16, [len(rows)])
-        assert torch.equal(part.forward(small, h[rows].cuda()), got[rows])
+        alone = part.forward(small, h[rows].cuda())
+        assert torch.equal(alone, legacy[rows])
+        np.testing.assert_allclose(alone.double().cpu().numpy() / scale, got[rows].double().cpu().numpy() / scale, atol=1e-2, rtol=0)
 
 
 def step_mixers(runner, cache, mixers, portions, inputs):

@@ -338,7 +338,8 @@ def bench_moe_experts(args) -> dict:
     from ..parts import ops
 
     tokens, width, ff, experts, top = args.tokens, args.k, args.n, args.experts, args.top
-    ctx = make_ctx(list(range(tokens)), [0] * tokens, options={"moe": "plain"} if args.plain else {})
+    options = {"moe": "plain"} if args.plain else ({"moe_stages": args.stages} if args.stages else {})  # --stages: ring depth of the tcgen05 form
+    ctx = make_ctx(list(range(tokens)), [0] * tokens, options=options)
     ctx.dtype = torch.bfloat16
     h = torch.randn(tokens, width, device="cuda", dtype=torch.bfloat16)
     w_gate_up = torch.randn(experts, 2 * ff, width, device="cuda", dtype=torch.bfloat16) * width**-0.5

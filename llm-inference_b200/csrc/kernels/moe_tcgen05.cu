@@ -137,12 +137,14 @@ moe_tcgen05_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_const
   // Which tile exists and whose it is comes from the sort kernel in front.
   wait_for_predecessor();
   let_successor_start();
-  const int tile = blockIdx.x;
+  // Row blocks of W run fastest in the grid: neighbouring blocks share the tile's X rows, and the other tiles of the
+  // expert, which want the same rows of W, are in flight at the same time.
+  const int tile = blockIdx.y;
   if (tile >= *p.num_tiles) return;  // the whole block, before anything is allocated
   const int expert = p.tile_expert[tile];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int stages = p.stages;
-  const int n0 = blockIdx.y * kBlockRows;
+  const int n0 = blockIdx.x * kBlockRows;
   const int num_kb = (p.K + kBlockK - 1) / kBlockK;
   const int w_row = expert * p.rows_per_expert + n0;
   const int x_row = tile * kPlaces;
@@ -302,7 +304,7 @@ int launch_product(const CUtensorMap& w_map, const CUtensorMap& x_map, const Exp
   if (cudaFuncSetAttribute(moe_tcgen05_kernel<MATS>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess)
     return b200_fail("moe_tcgen05: cannot size shared memory (%zu bytes)", smem);
   cudaLaunchConfig_t config = {};
-  config.gridDim = dim3(max_tiles, (p.n_total + kBlockRows - 1) / kBlockRows);
+  config.gridDim = dim3((p.n_total + kBlockRows - 1) / kBlockRows, max_tiles);
   config.blockDim = dim3(kThreads);
   config.dynamicSmemBytes = smem;
   config.stream = stream;
@@ -340,11 +342,14 @@ B200_API int b200_moe_product_tcgen05(const void* weight, const void* x, const i
                                       int max_tiles, int experts, int rows_per_expert, int second_offset, int n_total, int K, int mats,
                                       float limit, void* out, int stages, int* err, cudaStream_t stream) {
   if (max_tiles == 0) return 0;
-  B200_REQUIRE(max_tiles > 0 && experts > 0 && rows_per_expert > 0 && n_total > 0 && K > 0 && K % 8 == 0 && (mats == 1 || mats == 2),
+  B200_REQUIRE(max_tiles > 0 && max_tiles <= 65535 && experts > 0 && rows_per_expert > 0 && n_total > 0 && K > 0 && K % 8 == 0 && (mats == 1 || mats == 2),
                "moe_product_tcgen05: bad sizes");
   B200_REQUIRE(mats == 1 || (second_offset > 0 && second_offset + n_total <= rows_per_expert && limit > 0.f), "moe_product_tcgen05: bad second matrix");
   B200_REQUIRE(reinterpret_cast<uintptr_t>(weight) % 16 == 0 && reinterpret_cast<uintptr_t>(x) % 16 == 0, "moe_product_tcgen05: operands must be 16-byte aligned");
-  if (stages <= 0) stages = mats == 2 ? 2 : 3;  // 96 KB either way: two blocks share an SM, one's epilogue runs beside the other's products
+  // Two stages: 96 KB (gate and up) or 64 KB (down) a block, so that two or three blocks share an SM and one's epilogue runs
+  // beside the others' products. Measured on a B200 (2,048 tokens, width 3,584, 32 experts, 4 a token): 630 us for both
+  // products with 2 stages, 815 with 3, 844 with 4.
+  if (stages <= 0) stages = 2;
   B200_REQUIRE(stages >= 2 && stages <= 6 && static_cast<size_t>(stages) * (mats + 1) * kTileBytes + 1024 <= 200 * 1024,
                "moe_product_tcgen05: %d stages do not fit", stages);
   CUtensorMap w_map, x_map;
